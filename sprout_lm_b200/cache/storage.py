@@ -88,12 +88,15 @@ class CacheStorage:
             self.values.append(torch.zeros((*shape[:3], spec.value_width), dtype=runtime.dtype, device=runtime.device)
                                if spec.value_width else None)
         self.states = []
+        def make(spec):
+            return torch.zeros((manager.state_slot_count, *spec.shape), dtype=spec.dtype, device=runtime.device)
         for spec in model.state_specs():
             if spec is None:
                 self.states.append(None)
+            elif isinstance(spec, (tuple, list)):
+                self.states.append(tuple(make(one) for one in spec))     # a mixer with several state tensors per request
             else:
-                self.states.append(torch.zeros((manager.state_slot_count, *spec.shape), dtype=spec.dtype,
-                                               device=runtime.device))
+                self.states.append(make(spec))
 
     def view(self, slot: int, ctx, write: bool):
         if self.keys[slot] is None:
@@ -109,5 +112,6 @@ class CacheStorage:
     def clear_state(self, slot: int) -> None:
         """Zero a state slot when a request takes it."""
         for buffer in self.states:
-            if buffer is not None:
-                buffer[slot].zero_()
+            for one in (buffer if isinstance(buffer, tuple) else (buffer,)):
+                if one is not None:
+                    one[slot].zero_()

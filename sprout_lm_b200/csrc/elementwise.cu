@@ -6,10 +6,10 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// x[t, :] = table[token[t], :] widened to float32 (the residual stream is float32).
+// x[t, :] = table[token[t], :] widened to float32 (the residual stream is float32), times `scale`.
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int hidden, int vocab, int* status) {
+                             float* __restrict__ out, int hidden, int vocab, float scale, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -20,17 +20,17 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
   }
   const TW* row = table + (size_t)token * hidden;
   float* dst = out + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]) * scale;
 }
 
 SPROUT_API int sprout_embed(const void* table, int table_dtype, const int* tokens, float* out,
-                            int num_tokens, int hidden, int vocab, int* status, cudaStream_t stream) {
+                            int num_tokens, int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(num_tokens > 0 && hidden > 0 && vocab > 0, "embed: sizes must be positive");
   SPROUT_REQUIRE(table && tokens && out && status, "embed: null pointer");
   if (table_dtype == SPROUT_F32)
-    sprout_launch(embed_kernel<float>, dim3(num_tokens), dim3(256), 0, stream, (const float*)table, tokens, out, hidden, vocab, status);
+    sprout_launch(embed_kernel<float>, dim3(num_tokens), dim3(256), 0, stream, (const float*)table, tokens, out, hidden, vocab, scale, status);
   else if (table_dtype == SPROUT_BF16)
-    sprout_launch(embed_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, tokens, out, hidden, vocab, status);
+    sprout_launch(embed_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, tokens, out, hidden, vocab, scale, status);
   else
     return sprout_fail("embed: unknown dtype %d", table_dtype);
   return sprout_check_launch("embed");

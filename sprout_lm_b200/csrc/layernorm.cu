@@ -1,6 +1,6 @@
 // Row kernels of layers that wrap every sublayer in two norms, all float32 arithmetic:
-//  * layernorm:      out = (x - mean) / sqrt(var + eps) * w, var the mean of the squared deviations
-//                    (no bias); rows may be selected by index.
+//  * layernorm:      out = (x - mean) / sqrt(var + eps) * w (+ b), var the mean of the squared deviations;
+//                    rows may be selected by index.
 //  * norm_add:       x += layernorm(y) * w_b, and, when asked, h = layernorm(x) * w_next of the new x:
 //                    the norm after a sublayer, the residual sum and the norm before the next
 //                    sublayer in one launch.
@@ -30,8 +30,8 @@ __device__ __forceinline__ void row_moments(const float* row, int width, float e
 
 template <typename TO>
 __global__ void __launch_bounds__(THREADS)
-layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO* __restrict__ out,
-                 const int* __restrict__ rows, int width, float eps) {
+layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, const float* __restrict__ bias,
+                 TO* __restrict__ out, const int* __restrict__ rows, int width, float eps) {
   extern __shared__ float smem[];
   float* row = smem;                 // width
   float* scratch = smem + width;     // 33
@@ -43,7 +43,7 @@ layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO
   float mean, rstd;
   row_moments(row, width, eps, scratch, mean, rstd);
   TO* dst = out + (size_t)blockIdx.x * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<TO>((row[i] - mean) * rstd * gain[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<TO>((row[i] - mean) * rstd * gain[i] + (bias ? bias[i] : 0.f));
 }
 
 template <typename TO>
@@ -99,8 +99,8 @@ __device__ __forceinline__ void warp_moments(const float4 (&v)[NV], float eps, f
 
 template <typename TO, int NV>
 __global__ void __launch_bounds__(128)
-layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO* __restrict__ out,
-                      const int* __restrict__ rows, int count, float eps) {
+layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain, const float* __restrict__ bias,
+                      TO* __restrict__ out, const int* __restrict__ rows, int count, float eps) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, row = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -115,8 +115,9 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gai
 #pragma unroll
   for (int i = 0; i < NV; i++) {
     const float4 g = ((const float4*)gain)[i * 32 + lane];
-    store_four<TO>(dst + (i * 32 + lane) * 4, (v[i].x - mean) * rstd * g.x, (v[i].y - mean) * rstd * g.y, (v[i].z - mean) * rstd * g.z,
-                   (v[i].w - mean) * rstd * g.w);
+    const float4 b = bias ? ((const float4*)bias)[i * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+    store_four<TO>(dst + (i * 32 + lane) * 4, (v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y,
+                   (v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
   }
 }
 
@@ -243,16 +244,16 @@ int grid_for(long long count) { return (int)((count + 255) / 256 < 148 * 8 ? (co
 
 }  // namespace
 
-SPROUT_API int sprout_layernorm(const float* x, const float* gain, void* out, int out_dtype, const int* rows, int count,
-                                int width, float eps, cudaStream_t stream) {
+SPROUT_API int sprout_layernorm(const float* x, const float* gain, const float* bias, void* out, int out_dtype, const int* rows,
+                                int count, int width, float eps, cudaStream_t stream) {
   SPROUT_REQUIRE(x && gain && out && count > 0 && width > 0 && eps > 0, "layernorm: bad arguments");
   SPROUT_REQUIRE(width <= 40000, "layernorm: rows of up to 40000 elements (got %d)", width);
   const int nv = vectors_per_lane(width);
-  if (nv && (out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16) && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0) {
+  if (nv && (out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16) && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)bias | (uintptr_t)out) & 15) == 0) {
     const dim3 grid((count + 3) / 4);
 #define CALL(N)                                                                                                                   \
-    if (out_dtype == SPROUT_F32) sprout_launch(layernorm_rows_kernel<float, N>, grid, dim3(128), 0, stream, x, gain, (float*)out, rows, count, eps); \
-    else sprout_launch(layernorm_rows_kernel<__nv_bfloat16, N>, grid, dim3(128), 0, stream, x, gain, (__nv_bfloat16*)out, rows, count, eps);
+    if (out_dtype == SPROUT_F32) sprout_launch(layernorm_rows_kernel<float, N>, grid, dim3(128), 0, stream, x, gain, bias, (float*)out, rows, count, eps); \
+    else sprout_launch(layernorm_rows_kernel<__nv_bfloat16, N>, grid, dim3(128), 0, stream, x, gain, bias, (__nv_bfloat16*)out, rows, count, eps);
     SPROUT_FOR_NV(nv, CALL)
 #undef CALL
     return sprout_check_launch("layernorm_rows");
@@ -260,10 +261,10 @@ SPROUT_API int sprout_layernorm(const float* x, const float* gain, void* out, in
   const size_t smem = (size_t)(width + 34) * sizeof(float);
   if (out_dtype == SPROUT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sprout_launch(layernorm_kernel<float>, dim3(count), dim3(THREADS), smem, stream, x, gain, (float*)out, rows, width, eps);
+    sprout_launch(layernorm_kernel<float>, dim3(count), dim3(THREADS), smem, stream, x, gain, bias, (float*)out, rows, width, eps);
   } else if (out_dtype == SPROUT_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sprout_launch(layernorm_kernel<__nv_bfloat16>, dim3(count), dim3(THREADS), smem, stream, x, gain, (__nv_bfloat16*)out, rows, width, eps);
+    sprout_launch(layernorm_kernel<__nv_bfloat16>, dim3(count), dim3(THREADS), smem, stream, x, gain, bias, (__nv_bfloat16*)out, rows, width, eps);
   } else {
     return sprout_fail("layernorm: unknown dtype %d", out_dtype);
   }

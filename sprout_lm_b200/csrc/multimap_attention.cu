@@ -29,17 +29,23 @@ namespace {
 constexpr int CHUNK = 128;
 constexpr int PARTS = 4;     // value elements per thread in the float32-arithmetic kernel: vdim <= PARTS * CHUNK
 
-// Row of a token: [q: q_vectors * dim | k: kv_heads * maps * dim | v: kv_heads * vdim] (k and v only when `write`).
+// Row of a token: [q: q_vectors * dim | k: kv_heads * maps * dim | v: kv_heads * vdim] (k and v only when `write`; no v
+// when `value_from_key`: the value row is then the key row as projected, before rotation and norm, and vdim = maps * dim).
+// A warp takes a vector: it rotates the first `rot` elements, then, with `unit_eps` > 0, divides the vector by its root
+// mean square over dim (float32; rounded once, on the way out).
+constexpr int ROPE_MAX_PER_LANE = 16;        // vectors of up to 512 elements
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 rope_maps_append_kernel(T* __restrict__ rows, int row_stride, const int* __restrict__ positions,
                         const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_stride,
                         const float* __restrict__ cos_table, const float* __restrict__ sin_table, int max_positions,
                         T* __restrict__ k_cache, T* __restrict__ v_cache, int q_vectors, int kv_heads, int maps, int dim,
-                        int rot, int vdim, int page_tokens, int num_pages, int write, int* status) {
+                        int rot, int vdim, int page_tokens, int num_pages, int write, float unit_eps, int value_from_key,
+                        int* status) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int pos = positions[t];
   T* row = rows + (size_t)t * row_stride;
   const int half = rot / 2;
@@ -47,40 +53,74 @@ rope_maps_append_kernel(T* __restrict__ rows, int row_stride, const int* __restr
   if (rot > 0 && !turn && threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
   const float* cs = cos_table + (size_t)(turn ? pos : 0) * half;
   const float* sn = sin_table + (size_t)(turn ? pos : 0) * half;
-  // queries: in place
-  if (turn) {
-    for (int i = threadIdx.x; i < q_vectors * half; i += blockDim.x) {
-      T* vec = row + (size_t)(i / half) * dim;
-      const int d = i % half;
-      const float u = to_float(vec[d]), v = to_float(vec[d + half]);
-      const float c = cs[d], s = sn[d];
-      vec[d] = from_float<T>(u * c - v * s);
-      vec[d + half] = from_float<T>(v * c + u * s);
+  int page = -1;
+  if (write) {
+    page = pos >= 0 ? block_table[(size_t)seq_of_token[t] * table_stride + pos / page_tokens] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
+      page = -1;
     }
   }
-  if (!write) return;
-  const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_tokens];
-  if (page < 0 || page >= num_pages) {
-    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
-    return;
-  }
-  const T* krow = row + (size_t)q_vectors * dim;
-  const T* vrow = krow + (size_t)kv_heads * maps * dim;
   const int kw = maps * dim;
-  for (int i = threadIdx.x; i < kv_heads * kw; i += blockDim.x) {
-    const int g = i / kw, e = i % kw, d = e % dim;
-    float value = to_float(krow[i]);
-    if (turn && d < rot) {
-      const int j = d < half ? d : d - half;
-      const float other = to_float(krow[i + (d < half ? half : -half)]);
-      value = d < half ? value * cs[j] - other * sn[j] : value * cs[j] + other * sn[j];
+  const int vectors = q_vectors + (write ? kv_heads * maps : 0);
+  for (int vec = warp; vec < vectors; vec += warps) {
+    const bool is_key = vec >= q_vectors;
+    if (is_key && page < 0) continue;
+    if (!is_key && !turn && unit_eps <= 0.f) continue;          // nothing to do to this query vector
+    T* src = row + (size_t)vec * dim;                             // the key vectors follow the query vectors
+    float vals[ROPE_MAX_PER_LANE], raw[ROPE_MAX_PER_LANE];
+    float squares = 0.f;
+#pragma unroll
+    for (int j = 0; j < ROPE_MAX_PER_LANE; j++) {
+      const int d = lane + 32 * j;
+      vals[j] = raw[j] = 0.f;
+      if (d < dim) {
+        float x = to_float(src[d]);
+        raw[j] = x;
+        if (turn && d < rot) {
+          const int i = d < half ? d : d - half;
+          const float other = to_float(src[d < half ? d + half : d - half]);
+          x = d < half ? x * cs[i] - other * sn[i] : x * cs[i] + other * sn[i];
+        }
+        vals[j] = x;
+        squares = fmaf(x, x, squares);
+      }
     }
-    k_cache[(((size_t)page * kv_heads + g) * page_tokens + pos % page_tokens) * kw + e] = from_float<T>(value);
+    float factor = 1.0f;
+    if (unit_eps > 0.f) factor = 1.0f / sqrtf(warp_sum(squares) / (float)dim + unit_eps);
+    __syncwarp();                                                 // every partner element was read before any is rewritten
+    if (!is_key) {
+#pragma unroll
+      for (int j = 0; j < ROPE_MAX_PER_LANE; j++)
+        if (lane + 32 * j < dim) src[lane + 32 * j] = from_float<T>(vals[j] * factor);
+      continue;
+    }
+    const int g = (vec - q_vectors) / maps, m = (vec - q_vectors) % maps;
+    const size_t at = ((size_t)page * kv_heads + g) * page_tokens + pos % page_tokens;
+#pragma unroll
+    for (int j = 0; j < ROPE_MAX_PER_LANE; j++) {
+      const int d = lane + 32 * j;
+      if (d < dim) {
+        k_cache[at * kw + m * dim + d] = from_float<T>(vals[j] * factor);
+        if (value_from_key) v_cache[at * vdim + m * dim + d] = from_float<T>(raw[j]);
+      }
+    }
   }
+  if (!write || page < 0 || value_from_key) return;
+  const T* vrow = row + (size_t)q_vectors * dim + (size_t)kv_heads * kw;
   for (int i = threadIdx.x; i < kv_heads * vdim; i += blockDim.x) {
     const int g = i / vdim, e = i % vdim;
     v_cache[(((size_t)page * kv_heads + g) * page_tokens + pos % page_tokens) * vdim + e] = vrow[i];
   }
+}
+
+// The first position that a query at `pos` sees: 0 (causal), pos - size + 1 (a window of `size` positions, itself
+// included) or the start of its chunk of `size` positions counted from position 0.
+enum MaskKind : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_CHUNK = 2 };
+__device__ __forceinline__ int first_visible(int kind, int size, int pos) {
+  if (kind == MASK_WINDOW) return max(0, pos - size + 1);
+  if (kind == MASK_CHUNK) return pos < 0 ? 0 : (pos / size) * size;
+  return 0;
 }
 
 template <typename T, int MAPS>
@@ -90,7 +130,8 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
                                  const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                  T* __restrict__ out, int out_stride, int heads, int kv_heads, int dim, int vdim,
                                  int page_tokens, int num_pages, float scale, float lambda, float norm_eps,
-                                 float out_scale, int* status) {
+                                 float out_scale, int mask_kind, int mask_size, const float* __restrict__ sink,
+                                 const T* __restrict__ gate, int gate_stride, int* status) {
   extern __shared__ float smem[];
   float* qs = smem;                                   // MAPS * dim
   float* probs = qs + MAPS * dim;                     // MAPS * CHUNK
@@ -115,9 +156,10 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
 #pragma unroll
     for (int part = 0; part < PARTS; part++) acc[m][part] = 0.f;
   }
-  for (int base = 0; base <= pos; base += CHUNK) {
+  const int lo = first_visible(mask_kind, mask_size, pos);
+  for (int base = (lo / CHUNK) * CHUNK; base <= pos; base += CHUNK) {
     const int p = base + tid;
-    bool valid = p <= pos;
+    bool valid = p >= lo && p <= pos;
     long long index = -1;
     if (valid) {
       const int page = table[p / page_tokens];
@@ -170,6 +212,18 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
     }
     __syncthreads();
   }
+  if (sink != nullptr) {
+    // one more term in every map's denominator: exp(sink_h), with no key and no value
+    const float extra = sink[h];
+#pragma unroll
+    for (int m = 0; m < MAPS; m++) {
+      const float top = fmaxf(m_run[m], extra);
+      const float keep = (m_run[m] == -INFINITY) ? 0.f : expf(m_run[m] - top);
+      l_run[m] = l_run[m] * keep + expf(extra - top);
+#pragma unroll
+      for (int part = 0; part < PARTS; part++) acc[m][part] *= keep;
+    }
+  }
   float o[PARTS];
   float squares = 0.f;
 #pragma unroll
@@ -180,6 +234,7 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
   }
   float factor = out_scale;
   if (norm_eps > 0.f) factor *= 1.0f / sqrtf(block_sum(squares, scratch) / (float)vdim + norm_eps);
+  if (gate != nullptr) factor *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + h])));
   T* dst = out + (size_t)t * out_stride + (size_t)h * vdim;
 #pragma unroll
   for (int part = 0; part < PARTS; part++)
@@ -202,6 +257,9 @@ struct MultiMapParams {
   // single-token steps may divide a request's tiles among `ksplit` CTAs (blockIdx.z); each then leaves its maxima, sums
   // and unnormalised accumulators in `partial` [requests, kv_heads, ksplit, 16 rows, maps, 2 + vdim] for the merge kernel
   int ksplit; float* partial;
+  // what a query sees (MaskKind and its size), an optional term exp(sink[head]) in every softmax denominator, and an
+  // optional gate: the head's output times sigmoid(gate[token * gate_stride + head])
+  int mask_kind, mask_size; const float* sink; const __nv_bfloat16* gate; int gate_stride;
 };
 
 template <int DIM, int VDIM, int MAPS, bool SPLIT>
@@ -212,7 +270,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   __nv_bfloat16* sQ = (__nv_bfloat16*)mm_smem;                   // MM_ROWS x KSTRIDE
   __nv_bfloat16* sK = sQ + MM_ROWS * KSTRIDE;                    // 2 x MM_KEYS x KSTRIDE
   __nv_bfloat16* sV = sK + 2 * MM_KEYS * KSTRIDE;                // 2 x MM_KEYS x VSTRIDE
-  __shared__ int s_token[MM_ROWS], s_head[MM_ROWS], s_limit[MM_ROWS];
+  __shared__ int s_token[MM_ROWS], s_head[MM_ROWS], s_limit[MM_ROWS], s_lo[MM_ROWS];
   __shared__ long long s_row[2][MM_KEYS];
 
   pdl_launch_dependents();
@@ -238,14 +296,17 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
       s_token[tid] = tok;
       s_head[tid] = g * group + gi % group;
       s_limit[tid] = p.positions[tok];
+      s_lo[tid] = first_visible(p.mask_kind, p.mask_size, s_limit[tid]);
     } else {
-      s_token[tid] = -1; s_head[tid] = 0; s_limit[tid] = -1;
+      s_token[tid] = -1; s_head[tid] = 0; s_limit[tid] = -1; s_lo[tid] = 0;
     }
   }
   __syncthreads();
   const int last_row = min(rows_total, row_base + MM_ROWS) - 1 - row_base;
   const int max_limit = s_limit[last_row];                          // positions grow with the row index
   const int kv_tiles = max_limit / MM_KEYS + 1;
+  const int min_lo = s_lo[0];                                       // the first key any row sees: lo grows with the position
+  const int tile_lo = min_lo / MM_KEYS;
 
   for (int idx = tid; idx < MM_ROWS * KCHUNKS; idx += MM_THREADS) {
     const int row = idx / KCHUNKS, c = idx % KCHUNKS;
@@ -257,7 +318,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
     if (tid < MM_KEYS) {
       const int key = t * MM_KEYS + tid;
       long long row = -1;
-      if (key <= max_limit) {
+      if (key >= min_lo && key <= max_limit) {
         const int page = table[key / p.page_tokens];
         if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
         else row = ((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens;
@@ -281,7 +342,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
       else *(uint4*)dst = make_uint4(0, 0, 0, 0);
     }
   };
-  const int first_tile = SPLIT ? (int)blockIdx.z : 0, tile_step = SPLIT ? p.ksplit : 1;    // this CTA's tiles: every tile_step-th
+  const int first_tile = tile_lo + (SPLIT ? (int)blockIdx.z : 0), tile_step = SPLIT ? p.ksplit : 1;    // this CTA's tiles: every tile_step-th
   if (first_tile < kv_tiles) find_rows(first_tile, 0);
   __syncthreads();
   if (first_tile < kv_tiles) load_tile(0);
@@ -296,6 +357,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   const int gr = lane >> 2, qc = lane & 3;
   const int my_row0 = qrow + gr, my_row1 = my_row0 + 8;
   const int limit0 = s_limit[my_row0], limit1 = s_limit[my_row1];
+  const int lo0 = s_lo[my_row0], lo1 = s_lo[my_row1];
   float m0[MAPS], m1[MAPS], l0[MAPS], l1[MAPS];
   float o[MAPS][VDIM / 8][4];
 #pragma unroll
@@ -307,6 +369,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   }
   const float scale_log2 = p.scale * 1.4426950408889634f;
   const int warp_min_limit = s_limit[min(qrow, last_row)];
+  const int warp_min_lo = s_lo[min(qrow, last_row)], warp_max_lo = s_lo[min(qrow + 15, last_row)];
 
   int buf = 1;
   for (int t = first_tile; t < kv_tiles; t += tile_step) {
@@ -320,7 +383,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
     const __nv_bfloat16* tK = sK + buf * MM_KEYS * KSTRIDE;
     const __nv_bfloat16* tV = sV + buf * MM_KEYS * VSTRIDE;
     const int kv0 = t * MM_KEYS;
-    if (kv0 + kb > s_limit[min(qrow + 15, last_row)]) continue;       // no row of this warp sees its keys of the tile
+    if (kv0 + kb > s_limit[min(qrow + 15, last_row)] || kv0 + kb + nk * 16 <= warp_min_lo) continue;   // no row of this warp sees its keys of the tile
 #pragma unroll
     for (int m = 0; m < MAPS; m++) {
       float s[MM_KEYS / 8][4];
@@ -349,6 +412,17 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
           if (key + 1 > limit0) s[i][1] = -INFINITY;
           if (key > limit1) s[i][2] = -INFINITY;
           if (key + 1 > limit1) s[i][3] = -INFINITY;
+        }
+      }
+      if (kv0 + kb < warp_max_lo) {                                  // keys before a row's window or chunk
+#pragma unroll
+        for (int i = 0; i < MM_KEYS / 8; i++) {
+          if (i >= 2 * nk) break;
+          const int key = kv0 + kb + i * 8 + qc * 2;
+          if (key < lo0) s[i][0] = -INFINITY;
+          if (key + 1 < lo0) s[i][1] = -INFINITY;
+          if (key < lo1) s[i][2] = -INFINITY;
+          if (key + 1 < lo1) s[i][3] = -INFINITY;
         }
       }
 #pragma unroll
@@ -466,6 +540,20 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
     }
     return;
   }
+  if (p.sink != nullptr) {
+    // exp(sink) joins every map's denominator: rescale to the larger of the running maximum and the sink
+    const float sk0 = p.sink[s_head[my_row0]] * 1.4426950408889634f, sk1 = p.sink[s_head[my_row1]] * 1.4426950408889634f;
+#pragma unroll
+    for (int m = 0; m < MAPS; m++) {
+      const float b0 = m0[m] == -INFINITY ? -INFINITY : m0[m] * scale_log2, b1 = m1[m] == -INFINITY ? -INFINITY : m1[m] * scale_log2;
+      const float t0 = fmaxf(b0, sk0), t1 = fmaxf(b1, sk1);
+      const float k0 = b0 == -INFINITY ? 0.f : exp2f(b0 - t0), k1 = b1 == -INFINITY ? 0.f : exp2f(b1 - t1);
+      l0[m] = l0[m] * k0 + exp2f(sk0 - t0);
+      l1[m] = l1[m] * k1 + exp2f(sk1 - t1);
+#pragma unroll
+      for (int i = 0; i < VDIM / 8; i++) { o[m][i][0] *= k0; o[m][i][1] *= k0; o[m][i][2] *= k1; o[m][i][3] *= k1; }
+    }
+  }
 #pragma unroll
   for (int m = 0; m < MAPS; m++) {
     inv0[m] = 1.0f / l0[m];
@@ -493,6 +581,10 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
     sq1 += __shfl_xor_sync(0xffffffffu, sq1, 1); sq1 += __shfl_xor_sync(0xffffffffu, sq1, 2);
     f0 *= 1.0f / sqrtf(sq0 / (float)VDIM + p.norm_eps);
     f1 *= 1.0f / sqrtf(sq1 / (float)VDIM + p.norm_eps);
+  }
+  if (p.gate != nullptr) {
+    if (s_token[my_row0] >= 0) f0 *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)s_token[my_row0] * p.gate_stride + s_head[my_row0]])));
+    if (s_token[my_row1] >= 0) f1 *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)s_token[my_row1] * p.gate_stride + s_head[my_row1]])));
   }
   if (s_token[my_row0] >= 0) {
     __nv_bfloat16* dst = p.out + (size_t)s_token[my_row0] * p.out_stride + (size_t)s_head[my_row0] * VDIM + qc * 2;
@@ -526,9 +618,15 @@ multimap_merge_kernel(const MultiMapParams p, int vdim) {
     float top = -INFINITY;
     for (int z = 0; z < p.ksplit; z++) top = fmaxf(top, base[z * share + m * (2 + vdim)]);
     float sum = 0.f, a[2] = {0.f, 0.f};
+    float top_log2 = top == -INFINITY ? -INFINITY : top * scale_log2;     // the shares' maxima are those of the unscaled scores
+    if (p.sink != nullptr) {
+      const float sk = p.sink[head] * 1.4426950408889634f;
+      top_log2 = fmaxf(top_log2, sk);
+      sum = exp2f(sk - top_log2);
+    }
     for (int z = 0; z < p.ksplit; z++) {
       const float* at = base + z * share + m * (2 + vdim);
-      const float f = at[0] == -INFINITY ? 0.f : exp2f((at[0] - top) * scale_log2);
+      const float f = at[0] == -INFINITY ? 0.f : exp2f(at[0] * scale_log2 - top_log2);
       sum = fmaf(at[1], f, sum);
 #pragma unroll
       for (int part = 0; part < 2; part++)
@@ -543,6 +641,7 @@ multimap_merge_kernel(const MultiMapParams p, int vdim) {
     if (threadIdx.x + part * 128 < vdim) squares = fmaf(v[part], v[part], squares);
   float factor = p.out_scale;
   if (p.norm_eps > 0.f) factor *= 1.0f / sqrtf(block_sum(squares, scratch) / (float)vdim + p.norm_eps);
+  if (p.gate != nullptr) factor *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)token * p.gate_stride + head])));
   __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * vdim;
 #pragma unroll
   for (int part = 0; part < 2; part++)
@@ -591,7 +690,8 @@ SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const 
                                              const int* positions, void* out, int out_stride, int requests, int tiles,
                                              int max_q_len, int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
                                              int num_pages, float scale, float lambda, float norm_eps, float out_scale,
-                                             int ksplit, float* partial, int* status, cudaStream_t stream) {
+                                             int ksplit, float* partial, int mask_kind, int mask_size, const float* sink,
+                                             const void* gate, int gate_stride, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && q_start && positions && out && status, "multimap_attention_mma: null pointer");
   SPROUT_REQUIRE(requests > 0 && tiles > 0 && max_q_len > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 &&
                  num_pages > 0, "multimap_attention_mma: bad sizes");
@@ -601,7 +701,11 @@ SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const 
   SPROUT_REQUIRE(kv_heads <= 65535, "multimap_attention_mma: too many key/value heads");
   MultiMapParams p{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
                    table_stride, q_start, positions, (__nv_bfloat16*)out, out_stride, requests, heads, kv_heads, page_tokens,
-                   num_pages, scale, lambda, norm_eps, out_scale, status, ksplit, partial};
+                   num_pages, scale, lambda, norm_eps, out_scale, status, ksplit, partial, mask_kind, mask_size, sink,
+                   (const __nv_bfloat16*)gate, gate_stride};
+  SPROUT_REQUIRE(mask_kind == MASK_CAUSAL || ((mask_kind == MASK_WINDOW || mask_kind == MASK_CHUNK) && mask_size > 0),
+                 "multimap_attention_mma: a window or a chunk needs a positive size");
+  SPROUT_REQUIRE(!gate || gate_stride >= heads, "multimap_attention_mma: gate rows hold a number per head");
   SPROUT_REQUIRE(ksplit >= 1 && ksplit <= 64 && (ksplit == 1 || (partial && max_q_len * (heads / kv_heads) <= 16)),
                  "multimap_attention_mma: keys are divided among CTAs in single-token steps only, with scratch for the shares");
   const bool split = max_q_len * (heads / kv_heads) <= 16;
@@ -619,23 +723,27 @@ SPROUT_API int sprout_rope_maps_append(void* rows, int row_stride, int dtype, co
                                        const int* block_table, int table_stride, const float* cos_table,
                                        const float* sin_table, int max_positions, void* k_cache, void* v_cache, int tokens,
                                        int q_vectors, int kv_heads, int maps, int dim, int rot, int vdim, int page_tokens,
-                                       int num_pages, int write, int* status, cudaStream_t stream) {
+                                       int num_pages, int write, float unit_eps, int value_from_key, int* status,
+                                       cudaStream_t stream) {
   SPROUT_REQUIRE(rows && positions && status && tokens > 0 && q_vectors > 0 && dim > 0 && maps > 0, "rope_maps_append: bad arguments");
   SPROUT_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dim, "rope_maps_append: the rotated width must be even and at most dim");
   SPROUT_REQUIRE(rot == 0 || (cos_table && sin_table && max_positions > 0), "rope_maps_append: tables are missing");
   SPROUT_REQUIRE(!write || (k_cache && v_cache && seq_of_token && block_table && kv_heads > 0 && vdim > 0 && page_tokens > 0 &&
                             num_pages > 0), "rope_maps_append: the cache is missing");
-  const int need = q_vectors * dim + (write ? kv_heads * (maps * dim + vdim) : 0);
+  SPROUT_REQUIRE(dim <= 32 * ROPE_MAX_PER_LANE, "rope_maps_append: vectors of up to %d elements (got %d)", 32 * ROPE_MAX_PER_LANE, dim);
+  SPROUT_REQUIRE(!value_from_key || vdim == maps * dim, "rope_maps_append: values that are the keys have the keys' width");
+  const int need = q_vectors * dim + (write ? kv_heads * (maps * dim + (value_from_key ? 0 : vdim)) : 0);
   SPROUT_REQUIRE(row_stride >= need, "rope_maps_append: rows of %d elements, %d needed", row_stride, need);
   if (dtype == SPROUT_F32)
     sprout_launch(rope_maps_append_kernel<float>, dim3(tokens), dim3(128), 0, stream, (float*)rows, row_stride, positions,
                   seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions, (float*)k_cache,
-                  (float*)v_cache, q_vectors, kv_heads, maps, dim, rot, vdim, page_tokens, num_pages, write, status);
+                  (float*)v_cache, q_vectors, kv_heads, maps, dim, rot, vdim, page_tokens, num_pages, write, unit_eps,
+                  value_from_key, status);
   else if (dtype == SPROUT_BF16)
     sprout_launch(rope_maps_append_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, (__nv_bfloat16*)rows, row_stride,
                   positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
                   (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, q_vectors, kv_heads, maps, dim, rot, vdim, page_tokens,
-                  num_pages, write, status);
+                  num_pages, write, unit_eps, value_from_key, status);
   else
     return sprout_fail("rope_maps_append: unknown dtype %d", dtype);
   return sprout_check_launch("rope_maps_append");
@@ -646,20 +754,25 @@ SPROUT_API int sprout_multimap_attention_simple(const void* q, int q_stride, con
                                                 const int* positions, void* out, int out_stride, int dtype, int tokens,
                                                 int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
                                                 int num_pages, float scale, float lambda, float norm_eps, float out_scale,
-                                                int* status, cudaStream_t stream) {
+                                                int mask_kind, int mask_size, const float* sink, const void* gate,
+                                                int gate_stride, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && seq_of_token && positions && out && status, "multimap_attention: null pointer");
   SPROUT_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 && num_pages > 0,
                  "multimap_attention: bad sizes");
   SPROUT_REQUIRE(maps == 1 || maps == 2, "multimap_attention: one or two maps per head (got %d)", maps);
   SPROUT_REQUIRE(dim > 0 && vdim > 0 && vdim <= PARTS * CHUNK, "multimap_attention: value rows of up to %d elements (got %d)", PARTS * CHUNK, vdim);
   SPROUT_REQUIRE(heads <= 65535, "multimap_attention: too many heads");
+  SPROUT_REQUIRE(mask_kind == MASK_CAUSAL || ((mask_kind == MASK_WINDOW || mask_kind == MASK_CHUNK) && mask_size > 0),
+                 "multimap_attention: a window or a chunk needs a positive size");
+  SPROUT_REQUIRE(!gate || gate_stride >= heads, "multimap_attention: gate rows hold a number per head");
   const size_t smem = (size_t)(maps * dim + maps * CHUNK + 36) * sizeof(float) + CHUNK * sizeof(long long);
   SPROUT_REQUIRE(smem <= 48 * 1024, "multimap_attention: key vectors too long (%d)", dim);
   dim3 grid(tokens, heads);
 #define LAUNCH(T, M)                                                                                                      \
   sprout_launch(multimap_attention_simple_kernel<T, M>, grid, dim3(CHUNK), smem, stream, (const T*)q, q_stride,           \
                 (const T*)k_cache, (const T*)v_cache, block_table, table_stride, seq_of_token, positions, (T*)out,        \
-                out_stride, heads, kv_heads, dim, vdim, page_tokens, num_pages, scale, lambda, norm_eps, out_scale, status)
+                out_stride, heads, kv_heads, dim, vdim, page_tokens, num_pages, scale, lambda, norm_eps, out_scale,    \
+                mask_kind, mask_size, sink, (const T*)gate, gate_stride, status)
   if (dtype == SPROUT_F32) {
     if (maps == 1) LAUNCH(float, 1); else LAUNCH(float, 2);
   } else if (dtype == SPROUT_BF16) {

@@ -29,7 +29,7 @@ class KernelError(RuntimeError):
 
 _P, _I, _F, _L = c_void_p, c_int, c_float, ctypes.c_longlong
 _SIGNATURES = {
-    "sprout_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "sprout_embed": [_P, _I, _P, _P, _I, _I, _I, _F, _P, _P],
     "sprout_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
     "sprout_swiglu": [_P, _P, _I, _I, _I, _I, _P],
     "sprout_rope_append": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -62,18 +62,22 @@ _SIGNATURES = {
     "sprout_latent_attention_mma_supported": [_I, _I],
     "sprout_depth_average": [_P, _P, _P, _I, _L, _P],
     "sprout_softcap": [_P, _F, _L, _P],
-    "sprout_layernorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "sprout_layernorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
     "sprout_norm_add": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
     "sprout_gated_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _I, _F, _P],
     "sprout_relu2": [_P, _P, _I, _L, _P],
     "sprout_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
-    "sprout_rope_maps_append": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
-    "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P, _P, _P],
+    "sprout_rope_maps_append": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _P, _P, _I, _P, _P],
+    "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P, _I, _I, _P, _P, _I, _P, _P],
     "sprout_multimap_attention_mma_supported": [_I, _I, _I],
     "sprout_decay_chunks": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_decay_chunks_supported": [_I, _I, _I],
     "sprout_decay_scan": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
+    "sprout_causal_conv": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_gated_group_norm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "sprout_scaled_sum": [_P, _P, _F, _P, _F, _L, _P],
     "sprout_moe_route": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "sprout_moe_arrange": [_P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_moe_up_plain": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
@@ -189,8 +193,8 @@ def _rows_contiguous(t, name):
 
 # ---------------------------------------------------------------------------------- wrappers
 
-def embed(table, tokens, out, status):
-    """out[t] = table[tokens[t]] widened to float32."""
+def embed(table, tokens, out, status, scale: float = 1.0):
+    """out[t] = table[tokens[t]] widened to float32, times ``scale``."""
     _rows_contiguous(table, "table")
     if not table.is_contiguous() or not out.is_contiguous():
         raise KernelError("embed: table and out must be contiguous")
@@ -198,7 +202,7 @@ def embed(table, tokens, out, status):
     if tokens.numel() != T or table.shape[1] != H:
         raise KernelError("embed: shapes do not fit")
     _run("sprout_embed", _ptr(table, "table"), _dtype_code(table.dtype), _ptr(tokens, "tokens", torch.int32),
-         _ptr(out, "out", torch.float32), T, H, table.shape[0], _ptr(status, "status", torch.int32), _stream())
+         _ptr(out, "out", torch.float32), T, H, table.shape[0], float(scale), _ptr(status, "status", torch.int32), _stream())
 
 
 def rmsnorm(x, gain, out, eps, rows=None):
@@ -1089,14 +1093,18 @@ def softcap(x, cap: float):
 
 # ---------------------------------------------------------------------------------- layers wrapped in two norms, activations
 
-def layernorm(x, gain, out, eps: float, rows=None):
-    """out[r] = (x[r] - mean) / sqrt(var + eps) * gain of row r (or of row rows[r]); x float32, out float32 or bfloat16."""
+def layernorm(x, gain, out, eps: float, rows=None, bias=None):
+    """out[r] = (x[r] - mean) / sqrt(var + eps) * gain (+ bias) of row r (or of row rows[r]); x float32, out float32 or
+    bfloat16."""
     if x.dim() != 2 or out.dim() != 2 or not x.is_contiguous() or not out.is_contiguous():
         raise KernelError("layernorm: x and out must be contiguous 2-D")
     R, H = out.shape
     if x.shape[1] != H or gain.numel() != H or (rows is None and x.shape[0] != R) or (rows is not None and rows.numel() != R):
         raise KernelError("layernorm: shapes do not fit")
-    _run("sprout_layernorm", _ptr(x, "x", torch.float32), _ptr(gain, "gain", torch.float32), _ptr(out, "out"),
+    if bias is not None and bias.numel() != H:
+        raise KernelError("layernorm: the bias has one entry per column")
+    _run("sprout_layernorm", _ptr(x, "x", torch.float32), _ptr(gain, "gain", torch.float32),
+         _ptr(bias, "bias", torch.float32, allow_none=True), _ptr(out, "out"),
          _dtype_code(out.dtype), _ptr(rows, "rows", torch.int32, allow_none=True), R, H, float(eps), _stream())
 
 
@@ -1144,11 +1152,14 @@ def glu_clamped(gate_up, out, limit: float, alpha: float):
 # ---------------------------------------------------------------------------------- attention with one or two maps per head
 
 def rope_maps_append(rows, positions, seq_of_token, block_table, cos_table, sin_table, k_cache, v_cache, q_vectors: int,
-                     kv_heads: int, maps: int, dim: int, vdim: int, page_tokens: int, write: bool, status):
+                     kv_heads: int, maps: int, dim: int, vdim: int, page_tokens: int, write: bool, status,
+                     unit_eps: float = 0.0, value_from_key: bool = False):
     """Rotate the first ``2 * cos_table.shape[1]`` elements of every query vector (in place) and key vector by the token's
     position, half-split pairs; append keys ([pages, kv_heads, page_tokens, maps * dim]) and values
     ([pages, kv_heads, page_tokens, vdim]) when ``write``.  A row holds q_vectors * dim query elements, then (when
-    ``write``) kv_heads * maps * dim key elements and kv_heads * vdim value elements."""
+    ``write``) kv_heads * maps * dim key elements and kv_heads * vdim value elements.  With ``unit_eps`` > 0 every query
+    and key vector is divided by its root mean square over ``dim`` after the rotation; with ``value_from_key`` the rows hold
+    no value elements and the cached value row is the key row as projected (before rotation and norm)."""
     _rows_contiguous(rows, "rows")
     _rows_contiguous(block_table, "block_table")
     T = rows.shape[0]
@@ -1163,15 +1174,43 @@ def rope_maps_append(rows, positions, seq_of_token, block_table, cos_table, sin_
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0), cos_ptr, sin_ptr, max_positions,
          _ptr(k_cache, "k_cache", allow_none=not write), _ptr(v_cache, "v_cache", allow_none=not write), T, q_vectors,
          kv_heads, maps, dim, rot, vdim, page_tokens, k_cache.shape[0] if write else 1, 1 if write else 0,
-         _ptr(status, "status", torch.int32), _stream())
+         float(unit_eps), 1 if value_from_key else 0, _ptr(status, "status", torch.int32), _stream())
+
+
+MASK_KINDS = {"causal": 0, "window": 1, "chunk": 2}
+
+
+def _mask_code(mask) -> tuple[int, int]:
+    """(kind, size) of ``mask``: None or ("causal", None), ("window", n): a query sees itself and the n - 1 positions
+    before it, ("chunk", n): a query sees the positions of its own chunk of n, counted from position 0, up to itself."""
+    if mask is None:
+        return 0, 0
+    kind, size = mask
+    if kind not in MASK_KINDS or (kind != "causal" and (not isinstance(size, int) or size <= 0)):
+        raise KernelError(f"attention: unknown mask {mask!r}")
+    return MASK_KINDS[kind], int(size or 0)
+
+
+def _gate_args(gate, tokens: int, heads: int, dtype, name: str):
+    if gate is None:
+        return None, 0
+    if gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] != tokens or gate.shape[1] != heads or gate.dtype != dtype:
+        raise KernelError(f"{name}: the gate must be a [tokens, heads] view with unit inner stride, of q's dtype")
+    return gate.data_ptr(), gate.stride(0)
 
 
 def multimap_attention_simple(q, cache, ctx, out, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float,
-                              lam: float, norm_eps: float, out_scale: float, status):
+                              lam: float, norm_eps: float, out_scale: float, status, mask=None, sink=None, gate=None):
     """Causal attention with ``maps`` (1 or 2) softmax maps per head over shared values, float32 arithmetic:
     out = (a_0 - lam a_1) [/ rms when norm_eps > 0] * out_scale per head.  q [tokens, heads * maps * dim] (a view with
-    unit inner stride), out [tokens, heads * vdim]."""
+    unit inner stride), out [tokens, heads * vdim].  ``mask`` says what a query sees (``_mask_code``), ``sink`` (float32
+    [heads]) adds exp(sink_h) to every softmax denominator of head h, ``gate`` ([tokens, heads]) multiplies head h's output
+    by sigmoid(gate)."""
     _rows_contiguous(q, "q")
+    mask_kind, mask_size = _mask_code(mask)
+    gate_ptr, gate_stride = _gate_args(gate, q.shape[0], heads, q.dtype, "multimap_attention")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads):
+        raise KernelError("multimap_attention: one float32 sink per head")
     _rows_contiguous(out, "out")
     k_cache, v_cache = cache.k, cache.v
     if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype != q.dtype:
@@ -1184,8 +1223,8 @@ def multimap_attention_simple(q, cache, ctx, out, heads: int, kv_heads: int, map
          _ptr(cache.block_table, "block_table", torch.int32), cache.block_table.stride(0),
          _ptr(ctx.seq_of_token, "seq_of_token", torch.int32), _ptr(ctx.positions, "positions", torch.int32), _ptr(out, "out"),
          out.stride(0), _dtype_code(q.dtype), q.shape[0], heads, kv_heads, maps, dim, vdim, cache.page_tokens,
-         k_cache.shape[0], float(scale), float(lam), float(norm_eps), float(out_scale), _ptr(status, "status", torch.int32),
-         _stream())
+         k_cache.shape[0], float(scale), float(lam), float(norm_eps), float(out_scale), mask_kind, mask_size,
+         _ptr(sink, "sink", torch.float32, True), gate_ptr, gate_stride, _ptr(status, "status", torch.int32), _stream())
 
 
 # ---------------------------------------------------------------------------------- linear attention with decay and state
@@ -1279,8 +1318,14 @@ def multimap_key_split(requests: int, kv_heads: int, group: int, max_q_len: int,
     return max(1, min(8, tiles, -(-(sms or sm_count()) // ctas)))
 
 
+def visible_keys(mask, context: int) -> int:
+    """The most keys a query of a context of ``context`` positions sees under ``mask``, in whole 64-key tiles' reach."""
+    kind, size = _mask_code(mask)
+    return context if kind == 0 else min(context, size + 63)
+
+
 def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float, lam: float,
-                       norm_eps: float, out_scale: float, status):
+                       norm_eps: float, out_scale: float, status, mask=None, sink=None, gate=None):
     """Attention with one or two maps per head: the tensor-core kernel in bfloat16 for the sizes it is built for
     (``SPROUT_MULTIMAP_ATTENTION=simple`` keeps the float32-arithmetic kernel), else the float32-arithmetic kernel."""
     if q.dtype == torch.bfloat16 and os.environ.get("SPROUT_MULTIMAP_ATTENTION", "mma") != "simple" \
@@ -1300,7 +1345,11 @@ def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int,
         tiles = (q.shape[0] * group + 63) // 64 + requests
         max_q_len = int(getattr(ctx, "max_q_len", 0) or q.shape[0])
         planned = int(getattr(ctx, "planned_context", 0) or getattr(ctx, "max_context", 0) or 0)
-        ksplit = multimap_key_split(requests, kv_heads, group, max_q_len, planned) if planned else 1
+        ksplit = multimap_key_split(requests, kv_heads, group, max_q_len, visible_keys(mask, planned)) if planned else 1
+        mask_kind, mask_size = _mask_code(mask)
+        gate_ptr, gate_stride = _gate_args(gate, q.shape[0], heads, q.dtype, "multimap_attention")
+        if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads):
+            raise KernelError("multimap_attention: one float32 sink per head")
         partial = None
         if ksplit > 1:
             partial = torch.empty(requests * kv_heads * ksplit * 16 * maps * (2 + vdim), dtype=torch.float32, device=q.device)
@@ -1311,9 +1360,11 @@ def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int,
              out.stride(0), requests, tiles, max_q_len, heads, kv_heads, maps, dim, vdim,
              cache.page_tokens, k_cache.shape[0], float(scale),
              float(lam), float(norm_eps), float(out_scale), ksplit, _ptr(partial, "partial", torch.float32, True),
+             mask_kind, mask_size, _ptr(sink, "sink", torch.float32, True), gate_ptr, gate_stride,
              _ptr(status, "status", torch.int32), _stream())
         return
-    multimap_attention_simple(q, cache, ctx, out, heads, kv_heads, maps, dim, vdim, scale, lam, norm_eps, out_scale, status)
+    multimap_attention_simple(q, cache, ctx, out, heads, kv_heads, maps, dim, vdim, scale, lam, norm_eps, out_scale, status,
+                              mask=mask, sink=sink, gate=gate)
 
 
 CHUNKED_FROM = 8            # a step whose longest portion has at least this many tokens runs the chunked decay kernel
@@ -1369,6 +1420,89 @@ def moe_experts(h, order, offsets, w_gate_up, w_down, act, rows_out, experts: in
         return
     moe_up_plain(h, order, offsets, w_gate_up, act, experts, top, limit, alpha)
     moe_down_plain(act, offsets, w_down, rows_out, experts)
+
+
+# ---------------------------------------------------------------------------------- recurrences with a decay made from the input
+
+def _scan_view(t, name: str, width: int, dtype):
+    if t.dim() != 2 or t.stride(1) != 1 or t.shape[1] != width or t.dtype != dtype:
+        raise KernelError(f"gated_scan: {name} must be a [tokens, {width}] view with unit inner stride of {dtype}, got "
+                          f"{tuple(t.shape)} {t.dtype}")
+    return t.data_ptr(), t.stride(0)
+
+
+def gated_scan(q, k, v, z, bias, ctx, state, out, heads: int, groups: int, dim: int, vdim: int, status, per_head: bool = False,
+               tau: float = 1.0, q_scale: float = 1.0, a_log=None, skip=None):
+    """Per request and head, token by token: S = diag(a) S + (c k) v^T, o = S^T (q_scale q) + skip_h v, the state float32
+    [slots, heads, dim, vdim] read and written at the requests' slots (``state``: a ``StateView``-like with ``buffer`` and
+    ``slots``).  q, k [tokens, groups * dim] (heads of a group share them), v [tokens, heads * vdim], views with unit inner
+    stride of one dtype.  Per key channel (default): z [tokens, heads * dim] (of that dtype or float32), a = sigmoid(z + bias)^(1 / tau), c = 1.
+    ``per_head``: z [tokens, heads], dt = softplus(z + bias), a = exp(-exp(a_log) dt) for all of the head's channels, c = dt.
+    out float32 [tokens, heads * vdim]."""
+    tokens, dtype = v.shape[0], v.dtype
+    q_ptr, q_stride = _scan_view(q, "q", groups * dim, dtype)
+    k_ptr, k_stride = _scan_view(k, "k", groups * dim, dtype)
+    v_ptr, v_stride = _scan_view(v, "v", heads * vdim, dtype)
+    z_f32 = z.dtype == torch.float32                # the decay's input may be float32 beside bfloat16 projections
+    z_ptr, z_stride = _scan_view(z, "z", heads if per_head else heads * dim, torch.float32 if z_f32 else dtype)
+    buffer = state.buffer
+    if buffer.dtype != torch.float32 or not buffer.is_contiguous() or tuple(buffer.shape[1:]) != (heads, dim, vdim):
+        raise KernelError("gated_scan: state must be contiguous float32 [slots, heads, dim, vdim]")
+    if not out.is_contiguous() or out.dtype != torch.float32 or tuple(out.shape) != (tokens, heads * vdim):
+        raise KernelError("gated_scan: out must be contiguous float32 [tokens, heads * vdim]")
+    if bias.numel() != (heads if per_head else heads * dim) or (per_head and (a_log is None or a_log.numel() != heads)) \
+            or (skip is not None and skip.numel() != heads):
+        raise KernelError("gated_scan: the decay's constants do not fit the heads")
+    _run("sprout_gated_scan", q_ptr, q_stride, k_ptr, k_stride, v_ptr, v_stride, z_ptr, z_stride, 1 if z_f32 else 0,
+         _dtype_code(dtype), _ptr(bias, "bias", torch.float32), _ptr(a_log, "a_log", torch.float32, True), _ptr(skip, "skip", torch.float32, True),
+         1.0 / float(tau), float(q_scale), 1 if per_head else 0, state.slots.numel(), heads, groups, dim, vdim,
+         _ptr(ctx.q_start, "q_start", torch.int32), _ptr(state.slots, "state_slots", torch.int32),
+         _ptr(buffer, "state", torch.float32), buffer.shape[0], _ptr(out, "out", torch.float32),
+         _ptr(status, "status", torch.int32), _stream())
+
+
+def causal_conv(rows, weight, bias, out, ctx, state, status, silu: bool = True):
+    """out[t, c] = act(bias[c] + sum_j weight[c, j] x[t - (taps - 1 - j), c]) per request, zeros before its first token;
+    ``rows`` and ``out`` are [tokens, channels] views with unit inner stride of one dtype, weight float32 [channels, taps];
+    the state float32 [slots, taps - 1, channels] holds each request's last taps - 1 inputs and is brought up to date."""
+    channels, taps = weight.shape
+    buffer = state.buffer
+    if rows.dim() != 2 or rows.stride(1) != 1 or out.stride(1) != 1 or rows.shape != out.shape or rows.shape[1] != channels \
+            or rows.dtype != out.dtype:
+        raise KernelError("causal_conv: rows and out must be [tokens, channels] views of one dtype")
+    if weight.dtype != torch.float32 or not weight.is_contiguous() or (bias is not None and bias.numel() != channels):
+        raise KernelError("causal_conv: weight must be contiguous float32 [channels, taps], one bias per channel")
+    if buffer.dtype != torch.float32 or not buffer.is_contiguous() or tuple(buffer.shape[1:]) != (taps - 1, channels):
+        raise KernelError("causal_conv: state must be contiguous float32 [slots, taps - 1, channels]")
+    _run("sprout_causal_conv", rows.data_ptr(), rows.stride(0), _ptr(weight, "weight", torch.float32),
+         _ptr(bias, "bias", torch.float32, True), out.data_ptr(), out.stride(0), _dtype_code(rows.dtype),
+         _ptr(ctx.q_start, "q_start", torch.int32), _ptr(state.slots, "state_slots", torch.int32),
+         _ptr(buffer, "state", torch.float32), buffer.shape[0], state.slots.numel(), int(ctx.max_q_len), channels, taps,
+         1 if silu else 0, _ptr(status, "status", torch.int32), _stream())
+
+
+def gated_group_norm(o, gate, weight, out, eps: float, groups: int = 1, gate_first: bool = False, silu: bool = True):
+    """Rows of ``o`` (float32 [rows, width]) in ``groups`` equal parts, each divided by its root mean square (eps inside
+    the root), times ``weight`` (float32; it repeats every weight.numel() elements: a weight per head, or one for the whole
+    row), times act(gate), act = silu or sigmoid; with ``gate_first`` the gate is applied before the norm.  ``gate`` is a
+    [rows, width] view with unit inner stride of out's dtype."""
+    _rows_contiguous(gate, "gate")
+    rows, width = o.shape
+    if not o.is_contiguous() or o.dtype != torch.float32 or not out.is_contiguous() or out.shape != o.shape \
+            or gate.shape != o.shape or gate.dtype != out.dtype or width % weight.numel() or width % groups:
+        raise KernelError("gated_group_norm: shapes or dtypes do not fit")
+    _run("sprout_gated_group_norm", _ptr(o, "o", torch.float32), _ptr(gate, "gate"), gate.stride(0),
+         _ptr(weight, "weight", torch.float32), weight.numel(), _ptr(out, "out"), _dtype_code(out.dtype), rows, width,
+         int(groups), float(eps), 1 if gate_first else 0, 1 if silu else 0, _stream())
+
+
+def scaled_sum(x, y1, a: float, y2=None, b: float = 0.0):
+    """x += a * y1 (+ b * y2), float32, element by element."""
+    if x.dtype != torch.float32 or not x.is_contiguous() or y1.shape != x.shape or not y1.is_contiguous() \
+            or (y2 is not None and (y2.shape != x.shape or not y2.is_contiguous())):
+        raise KernelError("scaled_sum: contiguous float32 tensors of one shape")
+    _run("sprout_scaled_sum", _ptr(x, "x", torch.float32), _ptr(y1, "y1", torch.float32), float(a),
+         _ptr(y2, "y2", torch.float32, True), float(b), x.numel(), _stream())
 
 
 def describe_status(word: int) -> str:

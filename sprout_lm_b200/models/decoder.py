@@ -56,7 +56,7 @@ class DecoderModel:
         for decl in self.tensor_decls():
             count = 1
             for n in decl.shape:
-                count *= n
+                count *= n or 0          # a dimension that only the file gives: not counted
             total += count * (item if decl.init == "matrix" else 4)
         return total
 

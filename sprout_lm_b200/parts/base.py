@@ -16,8 +16,8 @@ Categories and what each must provide:
                      sine stand at [position, d]; pairs are (d, d + rotary_dim / 2), or (2d, 2d + 1)
                      when the part has a true attribute ``interleaved``.
 * ``mixer``:         ``cache_spec() -> CacheSpec | None`` (what it keeps per token),
-                     ``state_spec() -> StateSpec | None`` (what it keeps per request, of fixed
-                     size), ``forward(h, x, ctx, cache, state)``: reads the normed activations
+                     ``state_spec() -> StateSpec | tuple of StateSpec | None`` (what it keeps per request,
+                     of fixed size; with a tuple the ``StateView``'s buffer is a tuple of buffers), ``forward(h, x, ctx, cache, state)``: reads the normed activations
                      ``h``, adds its output to ``x`` in place.
 * ``feed_forward``:  ``forward(h, x, ctx)``: adds its output to ``x`` in place.
 * ``block``:         arranges a layer's norms, mixer and feed-forward:
@@ -122,9 +122,14 @@ class CacheView:
 
 @dataclass
 class StateView:
-    """A layer's state buffer [slots, *shape] and the slot of each request of the step."""
+    """A layer's state buffer [slots, *shape] (a tuple of them for a mixer that declared several) and the slot of each
+    request of the step."""
     buffer: torch.Tensor
     slots: torch.Tensor
+
+    def part(self, index: int) -> "StateView":
+        """The view of one buffer of a tuple."""
+        return StateView(self.buffer[index], self.slots)
 
 
 class Runtime:

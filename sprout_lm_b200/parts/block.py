@@ -1,5 +1,5 @@
 """Arrangements of a layer's parts.  ``pre_norm``: x += mixer(norm_0(x)); x += ffn(norm_1(x))
-(src/qwen.ts:164-200)."""
+(src/qwen.ts:164-200); a layer without a feed-forward (``feed_forward.kind == "none"``) is the first half alone."""
 from __future__ import annotations
 
 from ..config.specs import LayerSpec
@@ -9,14 +9,15 @@ from .base import Part, build_part, register_part
 @register_part("block", "pre_norm")
 class PreNormBlock(Part):
     def __init__(self, prefix: str, layer: LayerSpec):
-        if len(layer.norms) != 2:
-            raise ValueError("a pre_norm block has two norms")
+        self.has_ffn = layer.feed_forward.kind != "none"
+        if len(layer.norms) != (2 if self.has_ffn else 1):
+            raise ValueError("a pre_norm block has one norm per sublayer")
         self.norms = [build_part("norm", spec, prefix) for spec in layer.norms]
         self.mixer = build_part("mixer", layer.mixer, prefix)
-        self.feed_forward = build_part("feed_forward", layer.feed_forward, prefix)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, prefix) if self.has_ffn else None
 
     def parts(self):
-        return [*self.norms, self.mixer, self.feed_forward]
+        return [*self.norms, self.mixer, *([self.feed_forward] if self.has_ffn else [])]
 
     def tensor_decls(self):
         return [decl for part in self.parts() for decl in part.tensor_decls()]
@@ -30,6 +31,8 @@ class PreNormBlock(Part):
         fused = getattr(self.mixer, "forward_with_norm", None)
         if fused is None or not fused(self.norms[0], x, ctx, cache, state):
             self.mixer.forward(self.norms[0].forward(x), x, ctx, cache, state)
+        if not self.has_ffn:
+            return
         fused = getattr(self.feed_forward, "forward_with_norm", None)
         if fused is None or not fused(self.norms[1], x, ctx):
             self.feed_forward.forward(self.norms[1].forward(x), x, ctx)

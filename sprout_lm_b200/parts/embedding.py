@@ -1,4 +1,4 @@
-"""Token embedding (a row copy, no scaling: src/qwen.ts:162-163) and the output head
+"""Token embedding (a row copy, src/qwen.ts:162-163; ``scale`` multiplies the rows when a model asks for it) and the output head
 (logits = W h, no bias; W is the embedding matrix itself when tied: src/qwen.ts:152,203).
 With ``softcap`` the head's logits become softcap * tanh(logits / softcap)."""
 from __future__ import annotations
@@ -12,8 +12,9 @@ from .linear import Linear
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, name: str = "embed_tokens", suffix: str = ".weight"):
-        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, name: str = "embed_tokens", suffix: str = ".weight",
+                 scale: float = 1.0):
+        self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
         self.tensor_name = f"{prefix}{name}{suffix}"
         self.table = None
         self.runtime = None
@@ -27,7 +28,7 @@ class TokenEmbedding(Part):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         x = torch.empty((token_ids.numel(), self.hidden_size), dtype=torch.float32, device=token_ids.device)
-        kernels.embed(self.table, token_ids, x, self.runtime.status)
+        kernels.embed(self.table, token_ids, x, self.runtime.status, scale=self.scale)
         return x
 
 

@@ -152,6 +152,33 @@ class ClampedGLU:
         self.down.forward(act, residual=x)
 
 
+@register_part("feed_forward", "clamped_glu_mlp")
+class ClampedGLUMLP(Part):
+    """x += W_down (g' sigmoid(alpha g') (u' + 1)) with g' = min(W_gate h, limit), u' = clamp(W_up h, -limit, limit): the
+    dense form of the layer the routed experts are made of (``ClampedGLU``)."""
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702,
+                 names: dict | None = None):
+        if hidden_size <= 0 or intermediate_size <= 0 or limit <= 0:
+            raise ValueError("clamped_glu_mlp: sizes and limit must be positive")
+        self.hidden_size, self.intermediate_size, self.limit, self.alpha = hidden_size, intermediate_size, float(limit), float(alpha)
+        names = names or {"gate": "gate", "up": "up", "down": "down"}
+        self.names = {key: prefix + value for key, value in names.items()}
+        self.layer = None
+
+    def tensor_decls(self):
+        return [TensorDecl(self.names["gate"], (self.intermediate_size, self.hidden_size)),
+                TensorDecl(self.names["up"], (self.intermediate_size, self.hidden_size)),
+                TensorDecl(self.names["down"], (self.hidden_size, self.intermediate_size))]
+
+    def load(self, source: WeightSource):
+        gate, up, down = (source.raw(self.names[key]) for key in ("gate", "up", "down"))
+        self.layer = ClampedGLU(gate, up, down, self.limit, self.alpha, source)
+
+    def forward(self, h, x, ctx=None):
+        self.layer.forward(h, x)
+
+
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
     """A mixture of small feed-forward layers of which each token uses ``top``.

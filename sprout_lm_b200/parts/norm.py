@@ -41,27 +41,34 @@ class RMSNorm(Part):
 
 @register_part("norm", "layernorm")
 class LayerNorm(Part):
-    """out = (x - mean) / sqrt(var + eps) * w, var the mean of the squared deviations; a weight and no bias.
-    float32 arithmetic; the output has the compute dtype."""
+    """out = (x - mean) / sqrt(var + eps) * w (+ b), var the mean of the squared deviations.  ``bias_suffix`` names the
+    bias tensor (the weight's name plus the suffix); None: a weight and no bias.  float32 arithmetic; the output has the
+    compute dtype."""
     fused_kind = "layernorm"     # a block that sums and norms in one kernel may take gain and eps
 
-    def __init__(self, prefix: str, size: int, eps: float, name: str = "norm", suffix: str = ""):
+    def __init__(self, prefix: str, size: int, eps: float, name: str = "norm", suffix: str = "", bias_suffix: str | None = None):
         if eps <= 0:
             raise ValueError("layernorm: eps must be positive")
         self.size, self.eps = int(size), float(eps)
         self.tensor_name = f"{prefix}{name}{suffix}"
-        self.gain = None
+        self.bias_name = None if bias_suffix is None else self.tensor_name + bias_suffix
+        self.gain = self.bias = None
         self.out_dtype = None
 
     def tensor_decls(self):
-        return [TensorDecl(self.tensor_name, (self.size,), "gain")]
+        decls = [TensorDecl(self.tensor_name, (self.size,), "gain")]
+        if self.bias_name is not None:
+            decls.append(TensorDecl(self.bias_name, (self.size,), "bias"))
+        return decls
 
     def load(self, source: WeightSource):
         self.gain = source.vector(self.tensor_name)
+        if self.bias_name is not None:
+            self.bias = source.vector(self.bias_name)
         self.out_dtype = source.runtime.dtype
 
     def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         count = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((count, self.size), dtype=self.out_dtype, device=x.device)
-        kernels.layernorm(x, self.gain, out, self.eps, rows)
+        kernels.layernorm(x, self.gain, out, self.eps, rows, bias=self.bias)
         return out

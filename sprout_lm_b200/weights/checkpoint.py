@@ -31,6 +31,13 @@ class WeightError(ValueError):
         self.wrong_shape = tuple(wrong_shape)
 
 
+def shape_fits(expected, got) -> bool:
+    """Whether a stored shape is the declared one; a declared dimension of None is one that only the file gives and fits
+    any size."""
+    expected, got = tuple(expected), tuple(got)
+    return len(expected) == len(got) and all(e is None or e == g for e, g in zip(expected, got))
+
+
 class Checkpoint:
     def __init__(self, directory):
         self.directory = Path(directory).resolve()
@@ -84,12 +91,12 @@ class Checkpoint:
 
     def check(self, expected: dict[str, tuple[int, ...]], ignorable=()) -> None:
         """Raise one WeightError naming every missing tensor, every tensor no part asked for and
-        every tensor whose shape differs from the expected one."""
+        every tensor whose shape differs from the expected one (``shape_fits``)."""
         found = self.inventory()
         missing = [n for n in expected if found.get(n) is None]
         unexpected = [n for n in found if n not in expected and n not in ignorable]
         wrong = [(n, tuple(expected[n]), found[n][0]) for n in expected
-                 if found.get(n) is not None and tuple(found[n][0]) != tuple(expected[n])]
+                 if found.get(n) is not None and not shape_fits(expected[n], found[n][0])]
         if not (missing or unexpected or wrong):
             return
         lines = [f"Checkpoint {self.directory} does not fit the model:"]
@@ -113,7 +120,7 @@ class Checkpoint:
         handle = self._file(shard)
         if name not in handle.entries:
             raise WeightError(f"Missing tensor: {name}.", missing=[name])
-        if shape is not None and tuple(shape) != handle.shape(name):
+        if shape is not None and not shape_fits(shape, handle.shape(name)):
             raise WeightError(f"Shape mismatch for {name}: expected {list(shape)}, got {list(handle.shape(name))}.",
                               wrong_shape=[name])
         return handle.tensor(name)

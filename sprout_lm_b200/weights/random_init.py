@@ -3,7 +3,7 @@ configuration and a seed.
 
 Which tensors exist, with which shapes, is asked of the model's own parts.  Matrices and
 biases are N(0, 0.02), norm gains 1 + N(0, 0.02) (``pass_last``: N(0, 0.02) with 1 added to the last entry;
-``polynomial``: 1/3 + N(0, 0.1) with a last entry of N(0, 0.1); ``wide``: N(0, 0.2)).  Every tensor has its own generator keyed
+``polynomial``: 1/3 + N(0, 0.1) with a last entry of N(0, 0.1); ``wide``: N(0, 0.2); ``conv``: N(0, 0.3)).  Every tensor has its own generator keyed
 by (seed, tensor name), so the values do not depend on the order of generation.  With
 ``dtype="bfloat16"`` (the default) matrices are rounded to bfloat16 and stored so, while gains
 and biases are stored in float32: the true 32-bit path and the bfloat16 path then read exactly
@@ -39,6 +39,8 @@ def random_tensor(seed: int, name: str, shape, init: str) -> torch.Tensor:
         values.reshape(-1)[:-1] += np.float32(1.0 / 3.0)               # mixing coefficients of comparable size, then a constant
     elif init == "wide":
         values = values * np.float32(10.0)                              # N(0, 0.2): small vectors whose products must show
+    elif init == "conv":
+        values = values * np.float32(15.0)                              # N(0, 0.3): a few taps per channel
     elif init not in ("matrix", "bias"):
         raise ValueError(f"unknown init kind {init!r} for {name}")
     return torch.from_numpy(values)
