@@ -995,6 +995,208 @@ def timed_letanex(args) -> dict:
     return result
 
 
+RARUTAR_SHAPES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, left_dim=64, left_vdim=128, rotated=64, window=1024, chunk=2048,
+               state_heads=16, state_dim=128, state_vdim=128, tau=16.0, rank=32, ssm_heads=64, ssm_vdim=64, ssm_state=128,
+               ssm_groups=8, taps=4, norm_groups=8, ff=4096, vocab=32768),
+    "0.3b": dict(width=1024, heads=8, kv_heads=2, dim=128, left_dim=64, left_vdim=128, rotated=64, window=512, chunk=1024,
+                 state_heads=8, state_dim=128, state_vdim=128, tau=16.0, rank=16, ssm_heads=32, ssm_vdim=64, ssm_state=64,
+                 ssm_groups=4, taps=4, norm_groups=4, ff=2048, vocab=32768),
+}
+
+
+def rarutar_folders(shape: str, layers: int):
+    """(Rarutar folder, Letanex folder of equal size), random weights, written once.  Rarutar's layers in fours: chunked
+    attention whose values are its keys, windowed attention beside gated linear attention, a selective state space, the
+    pair again; all with the gated feed-forward.  Letanex beside it: two-map attention, linear attention with a fixed
+    decay, twice, with a dense feed-forward of as many weights (two matrices of 1.5 ff against three of ff)."""
+    from sprout_lm_b200 import parse_config, write_random_model
+    z = RARUTAR_SHAPES[shape]
+    mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                 "mask": {"size": z["chunk"]}, "rot": {"base": 500000.0, "dims": z["rotated"]}}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["left_dim"], "vdim": z["left_vdim"], "scale": z["left_dim"] ** -0.5,
+            "mask": {"size": z["window"]},
+            "rot": {"base": 500000.0, "dims": z["left_dim"], "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": z["state_heads"], "dim": z["state_dim"], "vdim": z["state_vdim"], "tau": z["tau"], "rank": z["rank"]}
+    pair = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}
+    ssm = {"heads": z["ssm_heads"], "vdim": z["ssm_vdim"], "state": z["ssm_state"], "groups": z["ssm_groups"], "conv": z["taps"],
+           "norm_groups": z["norm_groups"]}
+    kinds = [("attention", attention), ("parallel", pair), ("mamba2", ssm), ("parallel", pair)]
+    raw = {"architecture": "Rarutar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+           "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(layers)], "max_positions": 16384}
+    entries = []
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["left_dim"], "vdim": z["left_vdim"], "scale": z["left_dim"] ** -0.5,
+                     "diff": 0.5, "rot": {"base": 10000.0, "dims": z["left_dim"], "scaling": {"factor": 8.0}}}
+            entries.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": z["ff"] * 3 // 2}})
+        else:
+            decay = [float(1.0 - 2.0 ** (-5 - 3 * h / max(1, z["state_heads"] - 1))) for h in range(z["state_heads"])]
+            entries.append({"type": "lightning", "mlp": {"kind": "dense", "ff": z["ff"] * 3 // 2},
+                            "mixer": {"heads": z["state_heads"], "dim": z["state_dim"], "vdim": z["state_vdim"], "decay": decay}})
+    letanex = {"architecture": "Letanex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "layers": entries,
+               "max_positions": 16384}
+    folders = []
+    for tag, config in (("rarutar", raw), ("letanex", letanex)):
+        folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_rarutar_{shape}_{tag}_L{layers}"
+        if not (folder / "complete").exists():
+            print(f"[bench] writing random weights to {folder}", file=sys.stderr, flush=True)
+            write_random_model(folder, parse_config(config), seed=0)
+            (folder / "complete").write_text("ok")
+        folders.append(folder)
+    return folders[0], folders[1]
+
+
+def timed_rarutar_kernels(shape: str, tokens: int, batch: int, context: int, peak: dict) -> dict:
+    """The new design's kernels alone beside the like kernels of Letanex at equal sizes: attention with one map under a
+    window or in chunks (gate, sink, unit-norm vectors) beside the two-map kernel, over one prompt of ``tokens`` tokens
+    (executed FLOPs of the visible keys against the measured bf16 rate) and over ``batch`` single tokens with ``context``
+    keys held (bytes of the visible keys against the measured copy rate); the scan with a decay per key channel and the
+    one with a decay per head beside the linear attention with a fixed decay (bytes that must move against the copy
+    rate); the short convolution and the gated group norm (bytes against the copy rate)."""
+    import torch
+    from types import SimpleNamespace
+    from sprout_lm_b200 import kernels
+    z = RARUTAR_SHAPES[shape]
+    page = 16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = {}
+
+    def rand(*shape_, scale=1.0, dtype=torch.bfloat16):
+        return (torch.randn(*shape_, device="cuda", generator=g) * scale).to(dtype)
+
+    def ctx_for(requests, new, held):
+        return SimpleNamespace(seq_of_token=torch.arange(requests, dtype=torch.int32, device="cuda").repeat_interleave(new),
+                               positions=(torch.arange(new, dtype=torch.int32, device="cuda") + (held - new)).repeat(requests),
+                               q_start=(torch.arange(requests + 1, dtype=torch.int32, device="cuda") * new),
+                               context_lens=torch.full((requests,), held, dtype=torch.int32, device="cuda"), max_q_len=new,
+                               max_context=held, planned_context=0, num_seqs=requests, num_tokens=requests * new)
+
+    def visible(mask, position):
+        kind, size = mask
+        return min(position + 1, size) if kind == "window" else position % size + 1
+
+    heads, kv = z["heads"], z["kv_heads"]
+    variants = (("windowed", 1, z["left_dim"], z["left_vdim"], ("window", z["window"]), False),
+                ("chunked_sink", 1, z["dim"], z["dim"], ("chunk", z["chunk"]), True),
+                ("two_map", 2, z["left_dim"], z["left_vdim"], None, False))
+    for label, requests, new, held in (("prefill", 1, tokens, tokens), ("decode", batch, 1, context)):
+        pages = -(-held // page)
+        table = torch.full((requests, -(-pages // 64) * 64), -1, dtype=torch.int32, device="cuda")
+        table[:, :pages] = torch.randperm(requests * pages, device="cuda", generator=g).to(torch.int32).reshape(requests, pages)
+        ctx = ctx_for(requests, new, held)
+        for name, maps, dim, vdim, mask, extras in variants:
+            k2, v2 = rand(requests * pages + 1, kv, page, maps * dim), rand(requests * pages + 1, kv, page, vdim)
+            rows = rand(requests * new, heads * maps * dim + 8 * (-(-heads // 8)), scale=0.3)
+            q2, gate = rows[:, :heads * maps * dim], rows[:, heads * maps * dim:heads * maps * dim + heads]
+            o2 = torch.empty(requests * new, heads * vdim, dtype=torch.bfloat16, device="cuda")
+            view = SimpleNamespace(k=k2, v=v2, block_table=table, page_tokens=page, write=False)
+            sink = torch.zeros(heads, device="cuda") if extras else None
+            lam, eps = (0.4, 1e-5) if maps == 2 else (0.0, 0.0)
+            us = _median_us(lambda: kernels.multimap_attention(q2, view, ctx, o2, heads, kv, maps, dim, vdim, dim ** -0.5, lam, eps, 0.5, status,
+                                                               mask=mask, sink=sink, gate=None if maps == 2 else gate),
+                            repeats=3 if label == "prefill" else 10)
+            if label == "prefill":
+                seen = sum(visible(mask, p) for p in range(tokens)) if mask else tokens * (tokens + 1) // 2
+                flops = 2.0 * heads * (maps * dim + vdim) * seen
+                out[f"{name}_prefill"] = {"us": round(us, 1), "visible_pairs": seen, "tflops": round(flops / us / 1e6, 1),
+                                          "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3)}
+            else:
+                seen = visible(mask, context - 1) if mask else context
+                mb = batch * seen * kv * (maps * dim + vdim) * 2 / 1e6
+                out[f"{name}_decode"] = {"us": round(us, 1), "visible_keys": seen, "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                         "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    # recurrent mixers: a decay per key channel, a decay per head, and the fixed decay of the linear attention
+    sh, sd, sv = z["state_heads"], z["state_dim"], z["state_vdim"]
+    mh, mv, mn, mg = z["ssm_heads"], z["ssm_vdim"], z["ssm_state"], z["ssm_groups"]
+    for label, requests, new in (("prefill", 1, tokens), ("decode", batch, 1)):
+        ctx = ctx_for(requests, new, new)
+        n = requests * new
+        slots = torch.arange(requests, dtype=torch.int32, device="cuda")
+        rows = rand(n, sh * (2 * sd + sv), scale=0.5)
+        zed = rand(n, sh * sd, dtype=torch.float32)
+        bias = torch.full((sh * sd,), 3.0, device="cuda")
+        state = SimpleNamespace(buffer=torch.zeros(requests, sh, sd, sv, device="cuda"), slots=slots)
+        o = torch.empty(n, sh * sv, device="cuda")
+        us = _median_us(lambda: kernels.gated_scan(rows[:, :sh * sd], rows[:, sh * sd:2 * sh * sd], rows[:, 2 * sh * sd:], zed, bias, ctx, state, o,
+                                                   sh, sh, sd, sv, status, tau=z["tau"], q_scale=sd ** -0.5), repeats=3 if new > 1 else 10)
+        mb = (n * sh * ((2 * sd + sv) * 2 + sd * 4 + sv * 4) + 2 * requests * sh * sd * sv * 4) / 1e6
+        out[f"channel_decay_scan_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                              "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
+                                              "tflops": round(4.0 * n * sh * sd * sv / us / 1e6, 2)}
+        rows_l = rand(n, sh * (2 * sd + 2 * sv), scale=0.5)
+        decay = torch.full((sh,), 0.99, device="cuda")
+        state_l = SimpleNamespace(buffer=torch.zeros(requests, sh, sd, sv, device="cuda"), slots=slots)
+        us = _median_us(lambda: kernels.decay_attention(rows_l, ctx, state_l, decay, o, sh, sd, sv, True, status), repeats=3 if new > 1 else 10)
+        mb = (n * sh * ((2 * sd + sv) * 2 + sv * 4) + 2 * requests * sh * sd * sv * 4) / 1e6
+        out[f"fixed_decay_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                       "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
+                                       "tflops": round(4.0 * n * sh * sd * sv / us / 1e6, 2)}
+        inner, channels = mh * mv, mh * mv + 2 * mg * mn
+        proj = rand(n, inner + channels + 8 * (-(-mh // 8)), scale=0.5)
+        conv = torch.empty(n, channels, dtype=torch.bfloat16, device="cuda")
+        taps = z["taps"]
+        conv_state = SimpleNamespace(buffer=torch.zeros(requests, taps - 1, channels, device="cuda"), slots=slots)
+        weight, cbias = rand(channels, taps, scale=0.5, dtype=torch.float32), rand(channels, scale=0.1, dtype=torch.float32)
+        us = _median_us(lambda: kernels.causal_conv(proj[:, inner:inner + channels], weight, cbias, conv, ctx, conv_state, status, silu=True))
+        mb = (2 * n * channels * 2 + 2 * requests * (taps - 1) * channels * 4) / 1e6
+        out[f"short_conv_{label}"] = {"us": round(us, 1), "mb": round(mb, 2), "gbs": round(mb / us * 1e3),
+                                      "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+        ssm_state = SimpleNamespace(buffer=torch.zeros(requests, mh, mn, mv, device="cuda"), slots=slots)
+        y = torch.empty(n, inner, device="cuda")
+        dt_bias, a_log, skip = torch.zeros(mh, device="cuda"), torch.full((mh,), -2.0, device="cuda"), torch.ones(mh, device="cuda")
+        us = _median_us(lambda: kernels.gated_scan(conv[:, inner + mg * mn:], conv[:, inner:inner + mg * mn], conv[:, :inner],
+                                                   proj[:, inner + channels:inner + channels + mh], dt_bias, ctx, ssm_state, y, mh, mg, mn, mv,
+                                                   status, per_head=True, a_log=a_log, skip=skip), repeats=3 if new > 1 else 10)
+        mb = (n * (channels * 2 + mh * 2 + inner * 4) + 2 * requests * mh * mn * mv * 4) / 1e6
+        out[f"head_decay_scan_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                           "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
+                                           "tflops": round(4.0 * n * mh * mn * mv / us / 1e6, 2)}
+        gated = torch.empty(n, inner, dtype=torch.bfloat16, device="cuda")
+        gain = torch.ones(inner, device="cuda")
+        us = _median_us(lambda: kernels.gated_group_norm(y, proj[:, :inner], gain, gated, 1e-5, groups=z["norm_groups"], gate_first=True, silu=True))
+        mb = n * inner * (4 + 2 + 2) / 1e6
+        out[f"gated_group_norm_{label}"] = {"us": round(us, 1), "mb": round(mb, 2), "gbs": round(mb / us * 1e3),
+                                            "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    assert int(status.item()) == 0
+    return out
+
+
+def timed_rarutar(args) -> dict:
+    """``--only rarutar``: prefill and decode throughput of Rarutar at ``--shape 1b|0.3b`` (random weights, ``--layers``
+    layers, 4 if not given) beside Letanex at equal size, through the same runner, and the kernels of both alone."""
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.step import ModelRunner
+    shape = args.shape if args.shape in RARUTAR_SHAPES else "1b"
+    layers = args.layers or 4
+    peak = peaks()
+    rarutar_dir, letanex_dir = rarutar_folders(shape, layers)
+    prompt_len = args.prompt_len
+    result = {"impl": "ours", "only": "rarutar", "shape": shape, "layers": layers, "dtype": "bf16", "data": "synthetic",
+              "prefill_tokens": args.tokens, "decode_batch": args.batch, "decode_prompt_len": prompt_len, "steps": args.steps,
+              "peaks": {"bf16_tflops": peak["bf16_tflops"], "hbm_gbs": peak["hbm_gbs"], "source": peak.get("source", "measured")}}
+    for tag, folder in (("rarutar", rarutar_dir), ("letanex", letanex_dir)):
+        model = load_model(folder, dtype="bfloat16", device="cuda:0")
+        slots = max(64, args.batch)
+        pages = slots * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + args.tokens // 16 + 16
+        runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=slots, prefix_caching=False)
+        rng = np.random.default_rng(0)
+        ms = timed_prefill(runner, args.tokens, rng)
+        decode = timed_decode(runner, args.batch, prompt_len, args.steps, args.warmup, rng)
+        result[tag] = {"weights_mb": round((folder / "model.safetensors").stat().st_size / 1e6, 1), "prefill_ms": round(ms, 3),
+                       "prefill_tokens_per_s": round(args.tokens / ms * 1000),
+                       "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tokens_per_s"]),
+                       "decode_launches_per_step": decode["launches_per_step"]}
+        del runner, model
+        torch.cuda.empty_cache()
+    result["kernels"] = timed_rarutar_kernels(shape, args.tokens, max(args.batch, 64), 2048, peak)
+    return result
+
+
 def run(args) -> dict:
     import numpy as np
     import torch
@@ -1006,6 +1208,8 @@ def run(args) -> dict:
         return timed_latent(args)
     if args.only == "letanex":
         return timed_letanex(args)
+    if args.only == "rarutar":
+        return timed_rarutar(args)
     if args.only == "attention":
         return timed_attention(args.tokens, args.shape)
     if args.only == "gemm":
@@ -1113,9 +1317,9 @@ def main() -> int:
     parser.add_argument("--portion", type=int, default=4096, help="with --only long-prompt: tokens of a step (--tokens: of the whole prompt)")
     parser.add_argument("--prompt-len", type=int, default=512, help="with --only decode: tokens of every request's prompt (the context grows to hold it)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt", "latent", "letanex"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt", "latent", "letanex", "rarutar"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
-    parser.add_argument("--shape", choices=sorted(SHAPES) + sorted(LATENT_SHAPES), default="0.5b", help="with --only: the model's sizes")
+    parser.add_argument("--shape", choices=sorted(set(SHAPES) | set(LATENT_SHAPES) | set(LETANEX_SHAPES) | set(RARUTAR_SHAPES)), default="0.5b", help="with --only: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")
     parser.add_argument("--workload", choices=["mixed", "shared-prefix"], default="mixed",
                         help="with --only serve: mixed prompt lengths, or long prompts that share a prefix in a pool too small for all")

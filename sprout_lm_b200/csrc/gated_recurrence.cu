@@ -8,9 +8,9 @@
 //                    per head (a selective state space):      dt = softplus(z_t[h] + bias[h]), a_t[i] = exp(-exp(a_log[h]) dt),
 //                                                             c_t = dt.
 //                  q and k may be shared by the heads of a group (`groups` <= heads).  One block per (request, head,
-//                  block of value columns); thread j owns column j of the state; the next token's q, k and decays are
-//                  fetched while the current one is applied.  The order of operations per element is the tokens'
-//                  order: the result does not depend on the cutting or on the batch.
+//                  block of value columns) with its part of the state in registers; the tokens' vectors come through
+//                  shared memory a few tokens at a time.  The order of operations per element is the tokens' order:
+//                  the result does not depend on the cutting or on the batch.
 //  * causal_conv:  y_t[c] = act(bias[c] + sum_j w[c][j] x_(t - (taps - 1 - j))[c]), zeros before the start of the
 //                  sequence; the last taps - 1 inputs of a request live in its state slot [taps - 1, channels] and are
 //                  read at the start of a portion and replaced at its end.
@@ -43,65 +43,122 @@ struct ScanParams {
   int* status;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(128)
-gated_scan_kernel(const ScanParams<T> p) {
-  extern __shared__ float smem[];
-  const int cols = blockDim.x, dim = p.dim;
-  float* S = smem;                                   // dim * cols
-  float* token = S + (size_t)dim * cols;             // 2 buffers of [q | k | a], dim each
+constexpr int SCAN_THREADS = 128, SCAN_MAX_TOKENS = 8;
+
+// A block of SCAN_THREADS threads owns (request, head, `cb` value columns).  The state's rows are dealt to `slices`
+// lanes of a warp (a power of two): the thread of slice s and column c keeps rows s, s + slices, s + 2 slices, ... of
+// column c in ROWS registers, so the whole state of the block stays in registers from the first token to the last.
+// Tokens come `batch` at a time (batch * slices <= 64): while the threads walk a batch's tokens over their registers,
+// the next batch's q, k, decay inputs and values are on their way from memory into registers; at the batch's end
+// they are turned into float32 vectors in shared memory ([q_scale q | c k | a] per row).  The slices of a column add
+// their parts of o with shuffles.  Each element of S sees S <- fma(a, S, (c k) v) once per token in the tokens'
+// order, so the result does not depend on the cutting or on the batch.
+template <typename T, int ROWS>
+__global__ void __launch_bounds__(SCAN_THREADS)
+gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
+  constexpr int EPT = ROWS / 2;                      // row vectors a thread fetches per batch: batch * slices * ROWS / threads
+  constexpr int VPT = SCAN_MAX_TOKENS;               // values a thread fetches per batch: batch * cb / threads <= batch
+  extern __shared__ float4 scan_smem[];
+  const int slices = 1 << slices_log2, dim = p.dim;
+  const int rows_log2 = slices_log2 + (ROWS == 16 ? 4 : 5), rows_pad = 1 << rows_log2;
+  const int cb_log2 = 7 - slices_log2, cb = 1 << cb_log2;
+  float4* tok = scan_smem;                                             // [batch][rows_pad]: (q, k, a, -)
+  float* vt = reinterpret_cast<float*>(tok + (size_t)batch * rows_pad);  // [batch][cb]
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x, h = blockIdx.y;
-  const int col = blockIdx.z * cols + threadIdx.x;
+  const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int slice = tid & (slices - 1), col_local = tid >> slices_log2;
+  const int col = blockIdx.z * cb + col_local;
   const bool live = col < p.vdim;
   const int slot = p.state_slots[r];
   if (slot < 0 || slot >= p.num_slots) {
-    if (threadIdx.x == 0) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
+    if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
     return;
   }
   const int g = h / (p.heads / p.groups);
+  const bool per_head = p.mode == DECAY_PER_HEAD;
   float* mine = p.state + (((size_t)slot * p.heads + h) * dim) * p.vdim;
-  if (live)
-    for (int i = 0; i < dim; i++) S[i * cols + threadIdx.x] = mine[(size_t)i * p.vdim + col];
+  float S[ROWS];
+#pragma unroll
+  for (int j = 0; j < ROWS; j++) {
+    const int row = j * slices + slice;
+    S[j] = (live && row < dim) ? mine[(size_t)row * p.vdim + col] : 0.f;
+  }
   const float skip = p.skip ? p.skip[h] : 0.f;
-  const float rate = p.mode == DECAY_PER_HEAD ? expf(p.a_log[h]) : 0.f;
+  const float rate = per_head ? expf(p.a_log[h]) : 0.f;
   const int first = p.q_start[r], last = p.q_start[r + 1];
-
   auto z_at = [&](size_t index) { return p.z_f32 ? ((const float*)p.z)[index] : to_float(((const T*)p.z)[index]); };
-  auto fetch = [&](int t, float* buf) {
-    float step = 1.0f, decay = 1.0f;
-    if (p.mode == DECAY_PER_HEAD) {
-      step = softplus_f(z_at((size_t)t * p.z_stride + h) + p.bias[h]);
-      decay = expf(-rate * step);
-    }
-    for (int i = threadIdx.x; i < dim; i += cols) {
-      buf[i] = to_float(p.q[(size_t)t * p.q_stride + (size_t)g * dim + i]) * p.q_scale;
-      buf[dim + i] = to_float(p.k[(size_t)t * p.k_stride + (size_t)g * dim + i]) * step;
-      if (p.mode == DECAY_PER_CHANNEL) {
-        const float zv = z_at((size_t)t * p.z_stride + (size_t)h * dim + i) + p.bias[(size_t)h * dim + i];
-        decay = expf(-softplus_f(-zv) * p.inv_tau);              // sigmoid(z)^(1/tau) through its logarithm
+
+  float rq[EPT], rk[EPT], rz[EPT], rv[VPT];
+  auto fetch = [&](int t0) {                          // loads only: nothing waits for them here
+    const int n = min(batch, last - t0);
+#pragma unroll
+    for (int u = 0; u < EPT; u++) {
+      const int e = tid + u * SCAN_THREADS, tt = e >> rows_log2, i = e & (rows_pad - 1);
+      rq[u] = rk[u] = rz[u] = 0.f;
+      if (tt < n && i < dim) {
+        const size_t t = (size_t)(t0 + tt);
+        rq[u] = to_float(p.q[t * p.q_stride + (size_t)g * dim + i]);
+        rk[u] = to_float(p.k[t * p.k_stride + (size_t)g * dim + i]);
+        rz[u] = per_head ? z_at(t * p.z_stride + h) : z_at(t * p.z_stride + (size_t)h * dim + i);
       }
-      buf[2 * dim + i] = decay;
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; u++) {
+      const int e = tid + u * SCAN_THREADS, tt = e >> cb_log2, column = blockIdx.z * cb + (e & (cb - 1));
+      rv[u] = (tt < n && column < p.vdim) ? to_float(p.v[(size_t)(t0 + tt) * p.v_stride + (size_t)h * p.vdim + column]) : 0.f;
     }
   };
-  if (first < last) fetch(first, token);
-  for (int t = first; t < last; t++) {
-    float* cur = token + (size_t)((t - first) & 1) * 3 * dim;
-    __syncthreads();                                 // this token's vectors are there; the other buffer is free
-    if (t + 1 < last) fetch(t + 1, token + (size_t)((t + 1 - first) & 1) * 3 * dim);
-    if (!live) continue;
-    const float v = to_float(p.v[(size_t)t * p.v_stride + (size_t)h * p.vdim + col]);
-    float o = skip * v;
-    for (int i = 0; i < dim; i++) {
-      const float s = fmaf(cur[2 * dim + i], S[i * cols + threadIdx.x], cur[dim + i] * v);
-      S[i * cols + threadIdx.x] = s;
-      o = fmaf(s, cur[i], o);
+  if (first < last) fetch(first);
+  for (int t0 = first; t0 < last; t0 += batch) {
+    const int n = min(batch, last - t0);
+    __syncthreads();                                   // the batch before has been read by everyone
+#pragma unroll
+    for (int u = 0; u < EPT; u++) {
+      const int e = tid + u * SCAN_THREADS, tt = e >> rows_log2, i = e & (rows_pad - 1);
+      if (tt >= n) break;
+      float4 x = make_float4(0.f, 0.f, 1.f, 0.f);      // rows beyond dim stay zero
+      if (i < dim) {
+        float step = 1.0f, decay;
+        if (per_head) {
+          step = softplus_f(rz[u] + p.bias[h]);
+          decay = expf(-rate * step);
+        } else {
+          decay = expf(-softplus_f(-(rz[u] + p.bias[(size_t)h * dim + i])) * p.inv_tau);  // sigmoid(z)^(1/tau) through its logarithm
+        }
+        x.x = rq[u] * p.q_scale;
+        x.y = rk[u] * step;
+        x.z = decay;
+      }
+      tok[e] = x;
     }
-    p.out[(size_t)t * p.heads * p.vdim + (size_t)h * p.vdim + col] = o;
+#pragma unroll
+    for (int u = 0; u < VPT; u++) {
+      const int e = tid + u * SCAN_THREADS;
+      if (e < (n << cb_log2)) vt[e] = rv[u];
+    }
+    __syncthreads();
+    if (t0 + batch < last) fetch(t0 + batch);          // in flight while this batch is applied
+    for (int tt = 0; tt < n; tt++) {
+      const float v = vt[(tt << cb_log2) + col_local];
+      const float4* cur = tok + ((size_t)tt << rows_log2) + slice;
+      float o = 0.f;
+#pragma unroll
+      for (int j = 0; j < ROWS; j++) {
+        const float4 x = cur[j << slices_log2];
+        const float s = fmaf(x.z, S[j], x.y * v);
+        S[j] = s;
+        o = fmaf(s, x.x, o);
+      }
+      for (int d = slices >> 1; d > 0; d >>= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
+      if (slice == 0 && live) p.out[(size_t)(t0 + tt) * p.heads * p.vdim + (size_t)h * p.vdim + col] = fmaf(skip, v, o);
+    }
   }
-  if (live)
-    for (int i = 0; i < dim; i++) mine[(size_t)i * p.vdim + col] = S[i * cols + threadIdx.x];
+#pragma unroll
+  for (int j = 0; j < ROWS; j++) {
+    const int row = j * slices + slice;
+    if (live && row < dim) mine[(size_t)row * p.vdim + col] = S[j];
+  }
 }
 
 constexpr int CONV_MAX_TAPS = 8, CONV_TOKENS = 32;
@@ -213,16 +270,20 @@ __global__ void scaled_sum_kernel(float* __restrict__ x, const float* __restrict
 
 template <typename T>
 int launch_scan(const ScanParams<T>& p, int requests, cudaStream_t stream) {
-  int cols = p.vdim >= 128 ? 128 : (p.vdim + 31) / 32 * 32;
-  // the state's columns of a block and two sets of token vectors must fit shared memory
-  while (cols > 32 && ((size_t)p.dim * cols + 6 * p.dim) * sizeof(float) > 200 * 1024) cols -= 32;
-  const size_t smem = ((size_t)p.dim * cols + 6 * p.dim) * sizeof(float);
-  SPROUT_REQUIRE(smem <= 200 * 1024, "gated_scan: key vectors too long (%d)", p.dim);
-  if (smem > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(gated_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return sprout_fail("gated_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
-  }
-  sprout_launch(gated_scan_kernel<T>, dim3(requests, p.heads, (p.vdim + cols - 1) / cols), dim3(cols), smem, stream, p);
+  // rows per thread: 16 up to 512 key channels, 32 up to 1024; the slices of a column are lanes of one warp
+  const int rows = p.dim <= 16 * 32 ? 16 : 32;
+  SPROUT_REQUIRE(p.dim <= rows * 32, "gated_scan: key vectors too long (%d)", p.dim);
+  int slices_log2 = 0;
+  while ((rows << slices_log2) < p.dim) slices_log2++;
+  const int slices = 1 << slices_log2, cb = SCAN_THREADS / slices;
+  const int batch = 64 / slices < SCAN_MAX_TOKENS ? 64 / slices : SCAN_MAX_TOKENS;
+  const size_t smem = (size_t)batch * ((size_t)rows * slices * sizeof(float4) + (size_t)cb * sizeof(float));
+  const dim3 grid(requests, p.heads, (p.vdim + cb - 1) / cb);
+  SPROUT_REQUIRE(grid.z <= 65535, "gated_scan: too many value columns");
+  if (rows == 16)
+    sprout_launch(gated_scan_kernel<T, 16>, grid, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
+  else
+    sprout_launch(gated_scan_kernel<T, 32>, grid, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
   return sprout_check_launch("gated_scan");
 }
 

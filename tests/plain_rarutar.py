@@ -44,6 +44,38 @@ def read_safetensors(path) -> dict:
 
 
 # ------------------------------------------------------------------------------------------------ small pieces
+ROUND = None            # a function array -> array; set (see ``rounding``) to learn how far 16-bit matrix products move a result
+
+
+def to_bfloat16(a):
+    """Round to the nearest bfloat16 (ties to even), returned as float64."""
+    bits = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & np.uint32(0xFFFF0000)
+    return bits.view(np.float32).astype(np.float64)
+
+
+class rounding:
+    """``with rounding(to_bfloat16):`` every matrix product's input and output pass through the function."""
+
+    def __init__(self, fn):
+        self.fn = fn
+
+    def __enter__(self):
+        global ROUND
+        self.before, ROUND = ROUND, self.fn
+
+    def __exit__(self, *exc):
+        global ROUND
+        ROUND = self.before
+
+
+def lin(x, weight):
+    """W x for every row of x (weights are stored [out, in])."""
+    if ROUND is None:
+        return x @ weight.T
+    return ROUND(ROUND(x) @ weight.T)
+
+
 def sigmoid(z):
     return 1.0 / (1.0 + np.exp(-z))
 
@@ -129,18 +161,18 @@ def gated_softmax_mixer(h, w, prefix, m, eps, kind, unit_norm, value_is_key, has
     """Softmax attention with grouped heads, a rotation over part of each head, a mask of ``kind`` and a gate per head."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w[prefix + "q"].T).reshape(T, H, d)
-    k = (h @ w[prefix + "k"].T).reshape(T, G, d)
-    v = k.copy() if value_is_key else (h @ w[prefix + "v"].T).reshape(T, G, dv)
+    q = lin(h, w[prefix + "q"]).reshape(T, H, d)
+    k = lin(h, w[prefix + "k"]).reshape(T, G, d)
+    v = k.copy() if value_is_key else lin(h, w[prefix + "v"]).reshape(T, G, dv)
     positions = np.arange(T)
     q, k = rotate(q, positions, m["rot"]), rotate(k, positions, m["rot"])
     if unit_norm:
         q, k = rms_unit(q, eps), rms_unit(k, eps)
     sink = w[prefix + "sink"] if has_sink else None
     o = masked_softmax_attention(q, k, v, m["scale"], kind, m["mask"]["size"], sink)
-    gate = sigmoid(h @ w[prefix + "g"].T)                # [T, H]
+    gate = sigmoid(lin(h, w[prefix + "g"]))                # [T, H]
     o = o * gate[:, :, None]
-    return o.reshape(T, H * dv) @ w[prefix + "o"].T
+    return lin(o.reshape(T, H * dv), w[prefix + "o"])
 
 
 def gated_linear_attention(h, w, prefix, m, eps, state=None):
@@ -148,10 +180,10 @@ def gated_linear_attention(h, w, prefix, m, eps, state=None):
     each head's o is RMS-normed with a weight shared by the heads, then gated by silu(W_g h)."""
     T = h.shape[0]
     H, d, dv, tau = m["heads"], m["dim"], m["vdim"], float(m["tau"])
-    q = (h @ w[prefix + "q"].T).reshape(T, H, d) * d ** -0.5
-    k = (h @ w[prefix + "k"].T).reshape(T, H, d)
-    v = (h @ w[prefix + "v"].T).reshape(T, H, dv)
-    z = (h @ w[prefix + "a1"].T) @ w[prefix + "a2"].T + w[prefix + "a2.b"]
+    q = lin(h, w[prefix + "q"]).reshape(T, H, d) * d ** -0.5
+    k = lin(h, w[prefix + "k"]).reshape(T, H, d)
+    v = lin(h, w[prefix + "v"]).reshape(T, H, dv)
+    z = lin(lin(h, w[prefix + "a1"]), w[prefix + "a2"]) + w[prefix + "a2.b"]
     alpha = (sigmoid(z) ** (1.0 / tau)).reshape(T, H, d)
     S = np.zeros((H, d, dv)) if state is None else state
     o = np.zeros((T, H, dv))
@@ -159,7 +191,7 @@ def gated_linear_attention(h, w, prefix, m, eps, state=None):
         S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
         o[t] = np.einsum("hdv,hd->hv", S, q[t])
     o = rms_unit(o, eps) * w[prefix + "norm"]
-    out = (o.reshape(T, H * dv) * silu(h @ w[prefix + "g"].T)) @ w[prefix + "o"].T
+    out = lin(o.reshape(T, H * dv) * silu(lin(h, w[prefix + "g"])), w[prefix + "o"])
     return out, S
 
 
@@ -179,7 +211,7 @@ def mamba2_mixer(h, w, prefix, m, eps):
     T = h.shape[0]
     H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner = H * P
-    row = h @ w[prefix + "in"].T
+    row = lin(h, w[prefix + "in"])
     z, xbc, dt = row[:, :inner], row[:, inner:2 * inner + 2 * G * N], row[:, 2 * inner + 2 * G * N:]
     xbc = silu(causal_conv(xbc, w[prefix + "conv"], w[prefix + "conv.b"]))
     x = xbc[:, :inner].reshape(T, H, P)
@@ -197,14 +229,14 @@ def mamba2_mixer(h, w, prefix, m, eps):
     y = y.reshape(T, inner) * silu(z)
     parts = int(m["norm_groups"])
     y = rms_unit(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * w[prefix + "norm"]
-    return y @ w[prefix + "o"].T
+    return lin(y, w[prefix + "o"])
 
 
 def clamped_glu(h, w, prefix, mlp):
     limit = float(mlp["limit"])
-    g = np.minimum(h @ w[prefix + "gate"].T, limit)
-    u = np.clip(h @ w[prefix + "up"].T, -limit, limit)
-    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[prefix + "down"].T
+    g = np.minimum(lin(h, w[prefix + "gate"]), limit)
+    u = np.clip(lin(h, w[prefix + "up"]), -limit, limit)
+    return lin(g * sigmoid(1.702 * g) * (u + 1.0), w[prefix + "down"])
 
 
 # ------------------------------------------------------------------------------------------------ the model
@@ -234,4 +266,4 @@ def forward(config: dict, w: dict, tokens, layers_out: list | None = None):
         if layers_out is not None:
             layers_out.append(x.copy())
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
-    return x @ w["embed"].T
+    return lin(x, w["embed"])
