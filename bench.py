@@ -1108,7 +1108,20 @@ def timed_rarutar_kernels(shape: str, tokens: int, batch: int, context: int, pea
                 mb = batch * seen * kv * (maps * dim + vdim) * 2 / 1e6
                 out[f"{name}_decode"] = {"us": round(us, 1), "visible_keys": seen, "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
                                          "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
-    # recurrent mixers: a decay per key channel, a decay per head, and the fixed decay of the linear attention
+    # recurrent mixers: a decay per key channel, a decay per head, and the fixed decay of the linear attention.  The
+    # first two are 32-bit arithmetic on CUDA cores (the decays enter the recurrence in 32-bit), so beside the bytes
+    # their entries carry the share of the cores' nominal rate: SMs x 128 lanes x 2 x the highest SM clock; a token
+    # costs 3 operations per element of the state (a S + (c k) v, then q S), counted as 2 FLOPs each.
+    try:
+        top_mhz = float(subprocess.run(["nvidia-smi", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits", "-i", "0"],
+                                       capture_output=True, text=True, timeout=20).stdout.split()[0])
+    except (OSError, ValueError, IndexError, subprocess.SubprocessError):
+        top_mhz = 1965.0
+    fp32_tflops = torch.cuda.get_device_properties(0).multi_processor_count * 128 * 2 * top_mhz / 1e6
+    out["fp32_cuda_core_tflops_nominal"] = round(fp32_tflops, 1)
+
+    def of_cores(elements_tokens, us):
+        return round(3 * 2.0 * elements_tokens / us / 1e6 / fp32_tflops, 3)
     sh, sd, sv = z["state_heads"], z["state_dim"], z["state_vdim"]
     mh, mv, mn, mg = z["ssm_heads"], z["ssm_vdim"], z["ssm_state"], z["ssm_groups"]
     for label, requests, new in (("prefill", 1, tokens), ("decode", batch, 1)):
@@ -1125,7 +1138,8 @@ def timed_rarutar_kernels(shape: str, tokens: int, batch: int, context: int, pea
         mb = (n * sh * ((2 * sd + sv) * 2 + sd * 4 + sv * 4) + 2 * requests * sh * sd * sv * 4) / 1e6
         out[f"channel_decay_scan_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
                                               "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
-                                              "tflops": round(4.0 * n * sh * sd * sv / us / 1e6, 2)}
+                                              "tflops": round(4.0 * n * sh * sd * sv / us / 1e6, 2),
+                                              "of_nominal_fp32_cores": of_cores(n * sh * sd * sv, us)}
         rows_l = rand(n, sh * (2 * sd + 2 * sv), scale=0.5)
         decay = torch.full((sh,), 0.99, device="cuda")
         state_l = SimpleNamespace(buffer=torch.zeros(requests, sh, sd, sv, device="cuda"), slots=slots)
@@ -1153,7 +1167,8 @@ def timed_rarutar_kernels(shape: str, tokens: int, batch: int, context: int, pea
         mb = (n * (channels * 2 + mh * 2 + inner * 4) + 2 * requests * mh * mn * mv * 4) / 1e6
         out[f"head_decay_scan_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
                                            "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
-                                           "tflops": round(4.0 * n * mh * mn * mv / us / 1e6, 2)}
+                                           "tflops": round(4.0 * n * mh * mn * mv / us / 1e6, 2),
+                                           "of_nominal_fp32_cores": of_cores(n * mh * mn * mv, us)}
         gated = torch.empty(n, inner, dtype=torch.bfloat16, device="cuda")
         gain = torch.ones(inner, device="cuda")
         us = _median_us(lambda: kernels.gated_group_norm(y, proj[:, :inner], gain, gated, 1e-5, groups=z["norm_groups"], gate_first=True, silu=True))

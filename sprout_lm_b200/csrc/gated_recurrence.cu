@@ -41,35 +41,71 @@ struct ScanParams {
   const int* q_start; const int* state_slots; float* state; int num_slots;
   float* out;                          // [tokens, heads * vdim]
   int* status;
+  // portions cut into chunks (null / 0 when every request's tokens are walked by one block):
+  const float* da;                     // decays made beforehand: [tokens, heads * dim] per channel, [tokens, heads] per head
+  const float* dc;                     // per head: the factor on k, [tokens, heads]
+  float* sums;                         // [max_chunks, heads, dim, vdim]: a chunk's own sums, then the state before the chunk
+  float* prods;                        // [max_chunks, heads, dim]: the product of a chunk's decays
+  int chunk, requests;
 };
+
+// The chunks of all requests are numbered in the requests' order, ceil(tokens / chunk) each.  Finds chunk `index`:
+// its request, its place among the request's chunks and how many the request has; false beyond the last chunk.
+__device__ __forceinline__ bool find_chunk(const int* q_start, int requests, int chunk, int index, int& r, int& c, int& n) {
+  for (int i = 0; i < requests; i++) {
+    n = (q_start[i + 1] - q_start[i] + chunk - 1) / chunk;
+    if (index < n) { r = i; c = index; return true; }
+    index -= n;
+  }
+  return false;
+}
+
+enum ScanPhase : int { SCAN_WHOLE = 0, SCAN_CHUNK_SUMS = 1, SCAN_CHUNK_OUT = 2 };
 
 constexpr int SCAN_THREADS = 128, SCAN_MAX_TOKENS = 8;
 
-// A block of SCAN_THREADS threads owns (request, head, `cb` value columns).  The state's rows are dealt to `slices`
-// lanes of a warp (a power of two): the thread of slice s and column c keeps rows s, s + slices, s + 2 slices, ... of
-// column c in ROWS registers, so the whole state of the block stays in registers from the first token to the last.
-// Tokens come `batch` at a time (batch * slices <= 64): while the threads walk a batch's tokens over their registers,
-// the next batch's q, k, decay inputs and values are on their way from memory into registers; at the batch's end
-// they are turned into float32 vectors in shared memory ([q_scale q | c k | a] per row).  The slices of a column add
-// their parts of o with shuffles.  Each element of S sees S <- fma(a, S, (c k) v) once per token in the tokens'
-// order, so the result does not depend on the cutting or on the batch.
-template <typename T, int ROWS>
-__global__ void __launch_bounds__(SCAN_THREADS)
+// A block of SCAN_THREADS threads owns (request, head, `cb` value columns).  A thread keeps a tile of ROWS x COLS
+// elements of the state in registers from the first token to the last: the state's rows are dealt to `slices` lanes
+// of a warp (a power of two; the thread of slice s has rows s, s + slices, s + 2 slices, ...), the columns in groups of
+// COLS to the threads of equal slice, so every (q, k, a) triple read from shared memory serves COLS columns.
+// Tokens come `batch` at a time: while the threads walk a batch's tokens over their registers, the next batch's q, k,
+// decay inputs and values are on their way from memory into registers; at the batch's end they are turned into
+// float32 vectors in shared memory ([q_scale q | c k | a] per row).  The slices of a column add their parts of o with
+// shuffles.  Each element of S sees S <- fma(a, S, (c k) v) once per token in the tokens' order, so the result does not
+// depend on the cutting or on the batch.
+//
+// Long portions are cut into chunks of `p.chunk` tokens so that more blocks than (request, head, columns) have work, in
+// three launches: SCAN_CHUNK_SUMS walks every chunk but a request's last from a zero state and leaves the chunk's own
+// sums and the product of its decays; scan_carry_kernel turns them, in the chunks' order, into the state before each
+// chunk; SCAN_CHUNK_OUT walks every chunk from that state, writes the outputs, and the last chunk writes the
+// request's state.  The decays of these two walks are made beforehand by scan_decay_kernel (each is needed by all
+// blocks of columns and in both walks).  Against the single walk only the association of the decays' products
+// differs: (a_n ... a_1) S + sums instead of a_n (... (a_1 S)).
+template <typename T, int ROWS, int COLS, int PHASE>
+__global__ void __launch_bounds__(SCAN_THREADS, ROWS == 8 ? 4 : 2)
 gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
-  constexpr int EPT = ROWS / 2;                      // row vectors a thread fetches per batch: batch * slices * ROWS / threads
-  constexpr int VPT = SCAN_MAX_TOKENS;               // values a thread fetches per batch: batch * cb / threads <= batch
+  constexpr int ROWS_LOG2 = ROWS == 8 ? 3 : 5;
+  static_assert(ROWS == 8 || ROWS == 32, "rows of a thread's tile");
+  constexpr int EPT = ROWS == 8 ? 8 : 16;            // row vectors a thread fetches per batch: batch * slices * ROWS / threads
+  constexpr int VPT = SCAN_MAX_TOKENS;               // values a thread fetches per batch: batch * cb / threads
   extern __shared__ float4 scan_smem[];
   const int slices = 1 << slices_log2, dim = p.dim;
-  const int rows_log2 = slices_log2 + (ROWS == 16 ? 4 : 5), rows_pad = 1 << rows_log2;
-  const int cb_log2 = 7 - slices_log2, cb = 1 << cb_log2;
+  const int rows_log2 = slices_log2 + ROWS_LOG2, rows_pad = 1 << rows_log2;
+  const int cb_log2 = 7 - slices_log2 + (COLS == 4 ? 2 : 0), cb = 1 << cb_log2;
+  static_assert(COLS == 1 || COLS == 4, "columns of a thread's tile");
   float4* tok = scan_smem;                                             // [batch][rows_pad]: (q, k, a, -)
   float* vt = reinterpret_cast<float*>(tok + (size_t)batch * rows_pad);  // [batch][cb]
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int slice = tid & (slices - 1), col_local = tid >> slices_log2;
-  const int col = blockIdx.z * cb + col_local;
-  const bool live = col < p.vdim;
+  const int h = blockIdx.y, tid = threadIdx.x;
+  int r = blockIdx.x, chunk_at = 0, chunk_count = 1;
+  if (PHASE != SCAN_WHOLE) {
+    if (!find_chunk(p.q_start, p.requests, p.chunk, blockIdx.x, r, chunk_at, chunk_count)) return;
+    if (PHASE == SCAN_CHUNK_SUMS && chunk_at == chunk_count - 1) return;      // nothing comes after it
+  }
+  const bool last_chunk = chunk_at == chunk_count - 1;
+  const int slice = tid & (slices - 1), col_local = (tid >> slices_log2) * COLS;
+  const int col = blockIdx.z * cb + col_local;                          // the first of the thread's columns
   const int slot = p.state_slots[r];
   if (slot < 0 || slot >= p.num_slots) {
     if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
@@ -78,35 +114,62 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
   const int g = h / (p.heads / p.groups);
   const bool per_head = p.mode == DECAY_PER_HEAD;
   float* mine = p.state + (((size_t)slot * p.heads + h) * dim) * p.vdim;
-  float S[ROWS];
+  // the chunk's place in the scratch: the blocks before it belong to the requests before r and to r's earlier chunks
+  float* held = PHASE == SCAN_WHOLE ? nullptr : p.sums + (((size_t)(blockIdx.x) * p.heads + h) * dim) * p.vdim;
+  const float* from = (PHASE == SCAN_WHOLE || chunk_count == 1) ? mine : held;
+  const bool vectors = (p.vdim & 3) == 0;             // rows of the state start on 16-byte boundaries
+  float S[ROWS][COLS], P[PHASE == SCAN_CHUNK_SUMS ? ROWS : 1];
 #pragma unroll
   for (int j = 0; j < ROWS; j++) {
     const int row = j * slices + slice;
-    S[j] = (live && row < dim) ? mine[(size_t)row * p.vdim + col] : 0.f;
+    if (COLS == 4 && vectors) {                       // four columns of a row in one access
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (PHASE != SCAN_CHUNK_SUMS && col < p.vdim && row < dim) x = *reinterpret_cast<const float4*>(from + (size_t)row * p.vdim + col);
+      S[j][0] = x.x; S[j][1 % COLS] = x.y; S[j][2 % COLS] = x.z; S[j][3 % COLS] = x.w;
+    } else {
+#pragma unroll
+      for (int c = 0; c < COLS; c++)
+        S[j][c] = (PHASE != SCAN_CHUNK_SUMS && col + c < p.vdim && row < dim) ? from[(size_t)row * p.vdim + col + c] : 0.f;
+    }
+    if (PHASE == SCAN_CHUNK_SUMS) P[j] = 1.f;
   }
   const float skip = p.skip ? p.skip[h] : 0.f;
   const float rate = per_head ? expf(p.a_log[h]) : 0.f;
-  const int first = p.q_start[r], last = p.q_start[r + 1];
+  const int first = p.q_start[r] + chunk_at * (PHASE == SCAN_WHOLE ? 0 : p.chunk);
+  const int last = PHASE == SCAN_WHOLE ? p.q_start[r + 1] : min(p.q_start[r + 1], first + p.chunk);
   auto z_at = [&](size_t index) { return p.z_f32 ? ((const float*)p.z)[index] : to_float(((const T*)p.z)[index]); };
 
-  float rq[EPT], rk[EPT], rz[EPT], rv[VPT];
+  float rq[EPT], rk[EPT], rz[EPT], rc[PHASE == SCAN_WHOLE ? 1 : EPT], rv[VPT];
   auto fetch = [&](int t0) {                          // loads only: nothing waits for them here
     const int n = min(batch, last - t0);
+    // the batch's first rows once in 64-bit; within the batch 32-bit offsets do (at most SCAN_MAX_TOKENS rows further)
+    const size_t tb = (size_t)t0;
+    const T* qrow = p.q + tb * p.q_stride + (size_t)g * dim;
+    const T* krow = p.k + tb * p.k_stride + (size_t)g * dim;
+    const T* vrow = p.v + tb * p.v_stride + (size_t)h * p.vdim;
+    const float* arow = PHASE == SCAN_WHOLE ? nullptr : p.da + (per_head ? tb * p.heads + h : (tb * p.heads + h) * dim);
+    const float* crow = (PHASE == SCAN_WHOLE || !per_head) ? nullptr : p.dc + tb * p.heads + h;
 #pragma unroll
     for (int u = 0; u < EPT; u++) {
       const int e = tid + u * SCAN_THREADS, tt = e >> rows_log2, i = e & (rows_pad - 1);
       rq[u] = rk[u] = rz[u] = 0.f;
+      if (PHASE != SCAN_WHOLE) rc[u] = 0.f;
       if (tt < n && i < dim) {
-        const size_t t = (size_t)(t0 + tt);
-        rq[u] = to_float(p.q[t * p.q_stride + (size_t)g * dim + i]);
-        rk[u] = to_float(p.k[t * p.k_stride + (size_t)g * dim + i]);
-        rz[u] = per_head ? z_at(t * p.z_stride + h) : z_at(t * p.z_stride + (size_t)h * dim + i);
+        if (PHASE != SCAN_CHUNK_SUMS) rq[u] = to_float(qrow[tt * p.q_stride + i]);
+        rk[u] = to_float(krow[tt * p.k_stride + i]);
+        if (PHASE == SCAN_WHOLE) {
+          const size_t t = tb + tt;
+          rz[u] = per_head ? z_at(t * p.z_stride + h) : z_at(t * p.z_stride + (size_t)h * dim + i);
+        } else {
+          rz[u] = per_head ? arow[tt * p.heads] : arow[tt * p.heads * dim + i];
+          rc[u] = per_head ? crow[tt * p.heads] : 1.f;
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < VPT; u++) {
       const int e = tid + u * SCAN_THREADS, tt = e >> cb_log2, column = blockIdx.z * cb + (e & (cb - 1));
-      rv[u] = (tt < n && column < p.vdim) ? to_float(p.v[(size_t)(t0 + tt) * p.v_stride + (size_t)h * p.vdim + column]) : 0.f;
+      rv[u] = (tt < n && column < p.vdim) ? to_float(vrow[tt * p.v_stride + column]) : 0.f;
     }
   };
   if (first < last) fetch(first);
@@ -120,7 +183,10 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
       float4 x = make_float4(0.f, 0.f, 1.f, 0.f);      // rows beyond dim stay zero
       if (i < dim) {
         float step = 1.0f, decay;
-        if (per_head) {
+        if (PHASE != SCAN_WHOLE) {
+          step = rc[u];
+          decay = rz[u];
+        } else if (per_head) {
           step = softplus_f(rz[u] + p.bias[h]);
           decay = expf(-rate * step);
         } else {
@@ -139,26 +205,132 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
     }
     __syncthreads();
     if (t0 + batch < last) fetch(t0 + batch);          // in flight while this batch is applied
+    float* out_rows = p.out + (size_t)t0 * p.heads * p.vdim + (size_t)h * p.vdim + col;
     for (int tt = 0; tt < n; tt++) {
-      const float v = vt[(tt << cb_log2) + col_local];
+      float v[COLS], o[COLS];
+      if (COLS == 4) {
+        const float4 v4 = *reinterpret_cast<const float4*>(vt + (tt << cb_log2) + col_local);
+        v[0] = v4.x; v[1 % COLS] = v4.y; v[2 % COLS] = v4.z; v[3 % COLS] = v4.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < COLS; c++) v[c] = vt[(tt << cb_log2) + col_local + c];
+      }
+#pragma unroll
+      for (int c = 0; c < COLS; c++) o[c] = 0.f;
       const float4* cur = tok + ((size_t)tt << rows_log2) + slice;
-      float o = 0.f;
 #pragma unroll
       for (int j = 0; j < ROWS; j++) {
         const float4 x = cur[j << slices_log2];
-        const float s = fmaf(x.z, S[j], x.y * v);
-        S[j] = s;
-        o = fmaf(s, x.x, o);
+#pragma unroll
+        for (int c = 0; c < COLS; c++) {
+          const float s = fmaf(x.z, S[j][c], x.y * v[c]);
+          S[j][c] = s;
+          if (PHASE != SCAN_CHUNK_SUMS) o[c] = fmaf(s, x.x, o[c]);
+        }
+        if (PHASE == SCAN_CHUNK_SUMS) P[j] *= x.z;
       }
-      for (int d = slices >> 1; d > 0; d >>= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
-      if (slice == 0 && live) p.out[(size_t)(t0 + tt) * p.heads * p.vdim + (size_t)h * p.vdim + col] = fmaf(skip, v, o);
+      if (PHASE == SCAN_CHUNK_SUMS) continue;
+      float* dst = out_rows + tt * p.heads * p.vdim;
+      if (COLS == 4 && slices_log2 >= 2) {
+        // four sums over the slices with five shuffles instead of four per sum: neighbours split the columns between
+        // them (the even lane takes 0 and 1, the odd one 2 and 3), then pairs two apart split again; lane (b0, b1)
+        // ends with column 2 b0 + b1, added up over the remaining lanes as usual
+        const bool odd = slice & 1, upper = slice & 2;
+        float keep0 = odd ? o[2 % COLS] : o[0], keep1 = odd ? o[3 % COLS] : o[1 % COLS];
+        keep0 += __shfl_xor_sync(0xffffffffu, odd ? o[0] : o[2 % COLS], 1);
+        keep1 += __shfl_xor_sync(0xffffffffu, odd ? o[1 % COLS] : o[3 % COLS], 1);
+        float keep = upper ? keep1 : keep0;
+        keep += __shfl_xor_sync(0xffffffffu, upper ? keep0 : keep1, 2);
+        for (int d = 4; d < slices; d <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, d);
+        const int c = 2 * (slice & 1) + ((slice >> 1) & 1);
+        const float vc = c == 0 ? v[0] : c == 1 ? v[1 % COLS] : c == 2 ? v[2 % COLS] : v[3 % COLS];
+        if (slice < 4 && col + c < p.vdim) dst[c] = fmaf(skip, vc, keep);
+      } else {
+#pragma unroll
+        for (int c = 0; c < COLS; c++) {
+          for (int d = slices >> 1; d > 0; d >>= 1) o[c] += __shfl_xor_sync(0xffffffffu, o[c], d);
+          if (slice == 0 && col + c < p.vdim) dst[c] = fmaf(skip, v[c], o[c]);
+        }
+      }
     }
   }
+  if (PHASE == SCAN_CHUNK_OUT && !last_chunk) return;
+  float* to = PHASE == SCAN_CHUNK_SUMS ? held : mine;
 #pragma unroll
   for (int j = 0; j < ROWS; j++) {
     const int row = j * slices + slice;
-    if (live && row < dim) mine[(size_t)row * p.vdim + col] = S[j];
+    if (COLS == 4 && vectors) {
+      if (col < p.vdim && row < dim)
+        *reinterpret_cast<float4*>(to + (size_t)row * p.vdim + col) = make_float4(S[j][0], S[j][1 % COLS], S[j][2 % COLS], S[j][3 % COLS]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < COLS; c++)
+        if (col + c < p.vdim && row < dim) to[(size_t)row * p.vdim + col + c] = S[j][c];
+    }
+    if (PHASE == SCAN_CHUNK_SUMS && blockIdx.z == 0 && col_local == 0 && row < dim)
+      p.prods[((size_t)blockIdx.x * p.heads + h) * dim + row] = P[j];
   }
+}
+
+// The decays of every token of the step, once: per key channel a = sigmoid(z + bias)^(1 / tau); per head
+// dt = softplus(z + bias), a = exp(-exp(a_log) dt), c = dt.
+__global__ void scan_decay_kernel(const void* __restrict__ z, int z_stride, int z_f32, int is_bf16, const float* __restrict__ bias,
+                                  const float* __restrict__ a_log, float inv_tau, int mode, int heads, int dim, long long count,
+                                  float* __restrict__ da, float* __restrict__ dc) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_token = mode == DECAY_PER_HEAD ? heads : heads * dim;
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < count; e += (long long)gridDim.x * blockDim.x) {
+    const long long t = e / per_token;
+    const int c = (int)(e - t * per_token);
+    const size_t at = (size_t)t * z_stride + c;
+    const float zv = (z_f32 || !is_bf16) ? ((const float*)z)[at] : to_float(((const __nv_bfloat16*)z)[at]);
+    if (mode == DECAY_PER_HEAD) {
+      const float step = softplus_f(zv + bias[c]);
+      da[e] = expf(-expf(a_log[c]) * step);
+      dc[e] = step;
+    } else {
+      da[e] = expf(-softplus_f(-(zv + bias[c])) * inv_tau);
+    }
+  }
+}
+
+// In the chunks' order, per element of a request's state: the scratch's entry of chunk c (the chunk's own sums)
+// becomes the state before chunk c; requests of one chunk are left alone (their walk starts from the state slot).
+__global__ void scan_carry_kernel(float* __restrict__ sums, const float* __restrict__ prods, const float* __restrict__ state,
+                                  const int* __restrict__ q_start, const int* __restrict__ state_slots, int num_slots, int chunk,
+                                  int heads, int dim, int vdim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = (q_start[r + 1] - q_start[r] + chunk - 1) / chunk;
+  const int slot = state_slots[r];
+  if (n < 2 || e >= dim * vdim || slot < 0 || slot >= num_slots) return;
+  int base = 0;
+  for (int i = 0; i < r; i++) base += (q_start[i + 1] - q_start[i] + chunk - 1) / chunk;
+  const int row = e / vdim;
+  const size_t per = (size_t)heads * dim * vdim;
+  float* mine = sums + (size_t)base * per + (size_t)h * dim * vdim + e;
+  const float* decays = prods + ((size_t)base * heads + h) * dim + row;
+  float S = state[((size_t)slot * heads + h) * dim * vdim + e];
+  const size_t decay_step = (size_t)heads * dim;
+  for (int c0 = 0; c0 + 1 < n; c0 += 8) {              // eight chunks' loads are in flight before the first is used
+    float own[8], a[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const bool there = c0 + u + 1 < n;
+      own[u] = there ? mine[(size_t)(c0 + u) * per] : 0.f;
+      a[u] = there ? decays[(size_t)(c0 + u) * decay_step] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      if (c0 + u + 1 >= n) break;
+      mine[(size_t)(c0 + u) * per] = S;
+      S = fmaf(a[u], S, own[u]);
+    }
+  }
+  mine[(size_t)(n - 1) * per] = S;
 }
 
 constexpr int CONV_MAX_TAPS = 8, CONV_TOKENS = 32;
@@ -268,23 +440,42 @@ __global__ void scaled_sum_kernel(float* __restrict__ x, const float* __restrict
     x[i] += a * y1[i] + (y2 ? b * y2[i] : 0.f);
 }
 
-template <typename T>
-int launch_scan(const ScanParams<T>& p, int requests, cudaStream_t stream) {
-  // rows per thread: 16 up to 512 key channels, 32 up to 1024; the slices of a column are lanes of one warp
-  const int rows = p.dim <= 16 * 32 ? 16 : 32;
-  SPROUT_REQUIRE(p.dim <= rows * 32, "gated_scan: key vectors too long (%d)", p.dim);
+template <typename T, int ROWS, int COLS>
+int launch_scan_tiles(const ScanParams<T>& p, int requests, int max_chunks, cudaStream_t stream) {
   int slices_log2 = 0;
-  while ((rows << slices_log2) < p.dim) slices_log2++;
-  const int slices = 1 << slices_log2, cb = SCAN_THREADS / slices;
-  const int batch = 64 / slices < SCAN_MAX_TOKENS ? 64 / slices : SCAN_MAX_TOKENS;
-  const size_t smem = (size_t)batch * ((size_t)rows * slices * sizeof(float4) + (size_t)cb * sizeof(float));
+  while ((ROWS << slices_log2) < p.dim) slices_log2++;
+  SPROUT_REQUIRE(slices_log2 <= 5, "gated_scan: key vectors too long (%d)", p.dim);
+  const int slices = 1 << slices_log2, cb = SCAN_THREADS / slices * COLS;
+  // tokens of a batch: what a thread stages in registers bounds it (row vectors: ROWS * slices * batch / threads <= 8 or 16;
+  // values: cb * batch / threads <= SCAN_MAX_TOKENS)
+  int batch = SCAN_MAX_TOKENS;
+  const int by_rows = (ROWS == 8 ? 128 : 64) / slices, by_values = SCAN_MAX_TOKENS * slices / COLS;
+  if (batch > by_rows) batch = by_rows;
+  if (batch > by_values) batch = by_values;
+  const size_t smem = (size_t)batch * ((size_t)ROWS * slices * sizeof(float4) + (size_t)cb * sizeof(float));
   const dim3 grid(requests, p.heads, (p.vdim + cb - 1) / cb);
   SPROUT_REQUIRE(grid.z <= 65535, "gated_scan: too many value columns");
-  if (rows == 16)
-    sprout_launch(gated_scan_kernel<T, 16>, grid, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
-  else
-    sprout_launch(gated_scan_kernel<T, 32>, grid, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
-  return sprout_check_launch("gated_scan");
+  if (p.sums == nullptr) {
+    sprout_launch(gated_scan_kernel<T, ROWS, COLS, SCAN_WHOLE>, grid, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
+    return sprout_check_launch("gated_scan");
+  }
+  // `max_chunks` blocks per (head, columns): the chunks of all requests, found by their number
+  const dim3 chunks(max_chunks, p.heads, grid.z);
+  sprout_launch(gated_scan_kernel<T, ROWS, COLS, SCAN_CHUNK_SUMS>, chunks, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
+  if (int rc = sprout_check_launch("gated_scan (chunk sums)")) return rc;
+  SPROUT_REQUIRE(requests <= 65535, "gated_scan: too many requests");
+  sprout_launch(scan_carry_kernel, dim3((p.dim * p.vdim + 255) / 256, p.heads, requests), dim3(256), 0, stream, p.sums,
+                (const float*)p.prods, (const float*)p.state, p.q_start, p.state_slots, p.num_slots, p.chunk, p.heads, p.dim, p.vdim);
+  if (int rc = sprout_check_launch("gated_scan (carry)")) return rc;
+  sprout_launch(gated_scan_kernel<T, ROWS, COLS, SCAN_CHUNK_OUT>, chunks, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
+  return sprout_check_launch("gated_scan (chunk outputs)");
+}
+
+template <typename T>
+int launch_scan(const ScanParams<T>& p, int requests, int max_chunks, cudaStream_t stream) {
+  // a thread's tile of the state: 8 rows x 4 columns up to 256 key channels, 32 rows of one column up to 1024
+  if (p.dim <= 8 * 32) return launch_scan_tiles<T, 8, 4>(p, requests, max_chunks, stream);
+  return launch_scan_tiles<T, 32, 1>(p, requests, max_chunks, stream);
 }
 
 }  // namespace
@@ -293,8 +484,19 @@ SPROUT_API int sprout_gated_scan(const void* q, int q_stride, const void* k, int
                                  const void* z, int z_stride, int z_f32, int dtype, const float* bias, const float* a_log, const float* skip,
                                  float inv_tau, float q_scale, int mode, int requests, int heads, int groups, int dim, int vdim,
                                  const int* q_start, const int* state_slots, float* state, int num_slots, float* out, int* status,
+                                 int tokens, int chunk, int max_chunks, float* da, float* dc, float* sums, float* prods,
                                  cudaStream_t stream) {
   SPROUT_REQUIRE(q && k && v && z && bias && q_start && state_slots && state && out && status, "gated_scan: null pointer");
+  if (sums) {
+    // portions in chunks: scratch for the decays of every token and for every chunk's sums and decay product
+    SPROUT_REQUIRE(chunk > 0 && max_chunks > 0 && tokens > 0 && da && prods && (mode != DECAY_PER_HEAD || dc),
+                   "gated_scan: the chunked form needs its scratch");
+    const long long count = (long long)tokens * (mode == DECAY_PER_HEAD ? heads : heads * dim);
+    const long long blocks = (count + 255) / 256;
+    sprout_launch(scan_decay_kernel, dim3((unsigned)(blocks < 148 * 16 ? blocks : 148 * 16)), dim3(256), 0, stream, z, z_stride, z_f32,
+                  dtype == SPROUT_BF16 ? 1 : 0, bias, a_log, inv_tau, mode, heads, dim, count, da, dc);
+    if (int rc = sprout_check_launch("gated_scan (decays)")) return rc;
+  }
   SPROUT_REQUIRE(requests > 0 && heads > 0 && groups > 0 && heads % groups == 0 && dim > 0 && vdim > 0 && num_slots > 0,
                  "gated_scan: bad sizes");
   SPROUT_REQUIRE(mode == DECAY_PER_CHANNEL || (mode == DECAY_PER_HEAD && a_log), "gated_scan: unknown decay form");
@@ -302,14 +504,15 @@ SPROUT_API int sprout_gated_scan(const void* q, int q_stride, const void* k, int
   if (dtype == SPROUT_F32) {
     ScanParams<float> p{(const float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, z, z_stride, z_f32,
                         bias, a_log, skip, inv_tau, q_scale, mode, heads, groups, dim, vdim, q_start, state_slots, state,
-                        num_slots, out, status};
-    return launch_scan(p, requests, stream);
+                        num_slots, out, status, da, dc, sums, prods, chunk, requests};
+    return launch_scan(p, requests, max_chunks, stream);
   }
   if (dtype == SPROUT_BF16) {
     ScanParams<__nv_bfloat16> p{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
                                 v_stride, z, z_stride, z_f32, bias, a_log, skip, inv_tau, q_scale, mode, heads,
-                                groups, dim, vdim, q_start, state_slots, state, num_slots, out, status};
-    return launch_scan(p, requests, stream);
+                                groups, dim, vdim, q_start, state_slots, state, num_slots, out, status, da, dc, sums, prods, chunk,
+                                requests};
+    return launch_scan(p, requests, max_chunks, stream);
   }
   return sprout_fail("gated_scan: unknown dtype %d", dtype);
 }

@@ -74,7 +74,8 @@ _SIGNATURES = {
     "sprout_decay_chunks": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_decay_chunks_supported": [_I, _I, _I],
     "sprout_decay_scan": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
+    "sprout_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P,
+                          _I, _I, _I, _P, _P, _P, _P, _P],
     "sprout_causal_conv": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gated_group_norm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
     "sprout_scaled_sum": [_P, _P, _F, _P, _F, _L, _P],
@@ -1424,6 +1425,10 @@ def moe_experts(h, order, offsets, w_gate_up, w_down, act, rows_out, experts: in
 
 # ---------------------------------------------------------------------------------- recurrences with a decay made from the input
 
+SCAN_CHUNK = 64             # tokens of a chunk of the gated scan
+SCAN_CHUNKED_FROM = 128     # a step whose longest portion has at least this many tokens walks chunks side by side
+
+
 def _scan_view(t, name: str, width: int, dtype):
     if t.dim() != 2 or t.stride(1) != 1 or t.shape[1] != width or t.dtype != dtype:
         raise KernelError(f"gated_scan: {name} must be a [tokens, {width}] view with unit inner stride of {dtype}, got "
@@ -1438,7 +1443,9 @@ def gated_scan(q, k, v, z, bias, ctx, state, out, heads: int, groups: int, dim: 
     ``slots``).  q, k [tokens, groups * dim] (heads of a group share them), v [tokens, heads * vdim], views with unit inner
     stride of one dtype.  Per key channel (default): z [tokens, heads * dim] (of that dtype or float32), a = sigmoid(z + bias)^(1 / tau), c = 1.
     ``per_head``: z [tokens, heads], dt = softplus(z + bias), a = exp(-exp(a_log) dt) for all of the head's channels, c = dt.
-    out float32 [tokens, heads * vdim]."""
+    out float32 [tokens, heads * vdim].  A step whose longest portion has ``SCAN_CHUNKED_FROM`` tokens or more cuts the
+    portions into chunks of ``SCAN_CHUNK`` tokens that are walked side by side (``SPROUT_GATED_SCAN=whole`` keeps one walk
+    per request): scratch for every token's decay and every chunk's sums."""
     tokens, dtype = v.shape[0], v.dtype
     q_ptr, q_stride = _scan_view(q, "q", groups * dim, dtype)
     k_ptr, k_stride = _scan_view(k, "k", groups * dim, dtype)
@@ -1453,12 +1460,25 @@ def gated_scan(q, k, v, z, bias, ctx, state, out, heads: int, groups: int, dim: 
     if bias.numel() != (heads if per_head else heads * dim) or (per_head and (a_log is None or a_log.numel() != heads)) \
             or (skip is not None and skip.numel() != heads):
         raise KernelError("gated_scan: the decay's constants do not fit the heads")
+    global LAUNCHES
+    requests = state.slots.numel()
+    da = dc = sums = prods = None
+    max_chunks = 0
+    if getattr(ctx, "max_q_len", 1) >= SCAN_CHUNKED_FROM and os.environ.get("SPROUT_GATED_SCAN", "chunks") != "whole":
+        max_chunks = tokens // SCAN_CHUNK + requests
+        da = torch.empty(tokens * (heads if per_head else heads * dim), dtype=torch.float32, device=v.device)
+        dc = torch.empty(tokens * heads, dtype=torch.float32, device=v.device) if per_head else None
+        sums = torch.empty((max_chunks, heads, dim, vdim), dtype=torch.float32, device=v.device)
+        prods = torch.empty((max_chunks, heads, dim), dtype=torch.float32, device=v.device)
+        LAUNCHES += 3               # decays, chunk sums and the carry behind the same call
     _run("sprout_gated_scan", q_ptr, q_stride, k_ptr, k_stride, v_ptr, v_stride, z_ptr, z_stride, 1 if z_f32 else 0,
          _dtype_code(dtype), _ptr(bias, "bias", torch.float32), _ptr(a_log, "a_log", torch.float32, True), _ptr(skip, "skip", torch.float32, True),
          1.0 / float(tau), float(q_scale), 1 if per_head else 0, state.slots.numel(), heads, groups, dim, vdim,
          _ptr(ctx.q_start, "q_start", torch.int32), _ptr(state.slots, "state_slots", torch.int32),
          _ptr(buffer, "state", torch.float32), buffer.shape[0], _ptr(out, "out", torch.float32),
-         _ptr(status, "status", torch.int32), _stream())
+         _ptr(status, "status", torch.int32), tokens, SCAN_CHUNK, max_chunks, _ptr(da, "decays", torch.float32, True),
+         _ptr(dc, "steps", torch.float32, True), _ptr(sums, "sums", torch.float32, True), _ptr(prods, "products", torch.float32, True),
+         _stream())
 
 
 def causal_conv(rows, weight, bias, out, ctx, state, status, silu: bool = True):

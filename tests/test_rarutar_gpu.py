@@ -299,6 +299,72 @@ def _cut_three_ways(run, zero, inputs, wants, tol, cuts=(0, 2, 9, 10, 33)):
         assert np.abs(np.concatenate(pieces[i]) - wants[i]).max() <= tol * max(1.0, np.abs(wants[i]).max()), ("cut", i)
 
 
+def _plain_scan(q, k, v, a, c, S, skip):
+    """S_t = diag(a_t) S_(t-1) + (c_t k_t) v_t^T, o_t = S_t^T q_t + skip v_t for one head in float64; returns (o, S)."""
+    out = np.zeros((q.shape[0], v.shape[1]))
+    for t in range(q.shape[0]):
+        S = a[t][:, None] * S + np.outer(c[t] * k[t], v[t])
+        out[t] = S.T @ q[t] + skip * v[t]
+    return out, S
+
+
+# (heads, groups, dim, value dim, decay per head)
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [(3, 3, 24, 40, False), (2, 2, 128, 64, False), (4, 2, 16, 24, True), (2, 1, 64, 130, True), (1, 1, 520, 8, False)])
+def test_gated_scan_in_chunks(dtype, sizes, monkeypatch):
+    """Long portions walked as chunks side by side: requests of 300, 1, 129, 64 and 191 tokens in one batch (a last chunk
+    of one token, of a full chunk, requests of one chunk beside them), from states that are not zero, decays from very
+    fast to nearly one; against the recurrence in float64 and, in 32-bit, against the single walk of the same kernel."""
+    from sprout_lm_b200 import kernels
+    heads, groups, dim, vdim, per_head = sizes
+    rng = np.random.default_rng(dim + vdim)
+    lengths = [300, 1, 129, 64, 191]
+    total = sum(lengths)
+    q = rounded(rng.normal(0, 1.0, size=(total, groups * dim)), dtype)
+    k = rounded(rng.normal(0, 1.0, size=(total, groups * dim)), dtype)
+    v = rounded(rng.normal(0, 1.0, size=(total, heads * vdim)), dtype)
+    z = rounded(rng.normal(0, 2.0, size=(total, heads if per_head else heads * dim)), dtype)
+    bias = rounded(rng.uniform(-3.0, 1.0, size=heads) if per_head else rng.permutation(np.linspace(-3.0, 8.0, heads * dim)), "float32")
+    a_log = rounded(np.linspace(-5.0, 0.5, heads), "float32")
+    skip = rounded(rng.uniform(0.3, 1.5, size=heads), "float32")
+    tau, q_scale = 3.0, 0.5
+    start = rounded(rng.normal(0, 1.0, size=(6, heads, dim, vdim)), "float32")
+    slots = [4, 0, 5, 2, 1]
+    zf, bf = f64(z), f64(bias)
+    if per_head:
+        step = np.logaddexp(0.0, zf + bf)                                     # [tokens, heads]
+        decay = np.repeat(np.exp(-np.exp(f64(a_log)) * step)[:, :, None], dim, axis=2)
+    else:
+        step = np.ones((total, heads))
+        decay = (1.0 / (1.0 + np.exp(-(zf + bf))) ** (1.0 / tau)).reshape(total, heads, dim)
+    want, want_state, at = np.zeros((total, heads * vdim)), f64(start).copy(), 0
+    for n, slot in zip(lengths, slots):
+        for h in range(heads):
+            g = h // (heads // groups)
+            rows = slice(at, at + n)
+            o, S = _plain_scan(f64(q)[rows, g * dim:(g + 1) * dim] * q_scale, f64(k)[rows, g * dim:(g + 1) * dim], f64(v)[rows, h * vdim:(h + 1) * vdim],
+                               decay[rows, h], step[rows, h], want_state[slot, h], float(skip[h]) if per_head else 0.0)
+            want[rows, h * vdim:(h + 1) * vdim], want_state[slot, h] = o, S
+        at += n
+    ctx = SimpleNamespace(q_start=ints(np.concatenate([[0], np.cumsum(lengths)])), max_q_len=max(lengths))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    results = {}
+    for form in ("chunks", "whole"):
+        monkeypatch.setenv("SPROUT_GATED_SCAN", form)
+        state = SimpleNamespace(buffer=dev(start, "float32").clone(), slots=ints(slots))
+        out = torch.full((total, heads * vdim), float("nan"), device=DEV)
+        before = kernels.LAUNCHES
+        kernels.gated_scan(dev(q, dtype), dev(k, dtype), dev(v, dtype), dev(z, dtype), dev(bias, "float32"), ctx, state, out, heads, groups, dim, vdim,
+                           status, per_head=per_head, tau=tau, q_scale=q_scale, a_log=dev(a_log, "float32") if per_head else None,
+                           skip=dev(skip, "float32") if per_head else None)
+        assert kernels.LAUNCHES - before == (4 if form == "chunks" else 1)
+        results[form] = (out.cpu().numpy(), state.buffer.cpu().numpy())
+        for got, expected in zip(results[form], (want, want_state)):
+            assert np.abs(got - expected).max() <= 2e-5 * max(1.0, np.abs(expected).max()), (form, np.abs(got - expected).max())
+        assert np.array_equal(results[form][1][3], f64(start)[3].astype(np.float32))        # a slot of no request stays as it was
+    assert int(status.item()) == 0
+
+
 # (heads, dim, value dim, tau, inner size of the decay, width)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("sizes", [(3, 8, 20, 4.0, 5, 40), (1, 24, 8, 1.0, 3, 24), (4, 32, 64, 16.0, 8, 64), (2, 16, 130, 9.0, 7, 48),
