@@ -310,7 +310,8 @@ def _plain_scan(q, k, v, a, c, S, skip):
 
 # (heads, groups, dim, value dim, decay per head)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("sizes", [(3, 3, 24, 40, False), (2, 2, 128, 64, False), (4, 2, 16, 24, True), (2, 1, 64, 130, True), (1, 1, 520, 8, False)])
+@pytest.mark.parametrize("sizes", [(3, 3, 24, 40, False), (2, 2, 128, 64, False), (4, 2, 16, 24, True), (2, 1, 64, 130, True), (1, 1, 520, 8, False),
+                                   (2, 2, 200, 36, False), (2, 1, 136, 12, True), (1, 1, 5, 3, False)])
 def test_gated_scan_in_chunks(dtype, sizes, monkeypatch):
     """Long portions walked as chunks side by side: requests of 300, 1, 129, 64 and 191 tokens in one batch (a last chunk
     of one token, of a full chunk, requests of one chunk beside them), from states that are not zero, decays from very
