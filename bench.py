@@ -1017,7 +1017,7 @@ def rarutar_folders(shape: str, layers: int):
                  "mask": {"size": z["chunk"]}, "rot": {"base": 500000.0, "dims": z["rotated"]}}
     left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["left_dim"], "vdim": z["left_vdim"], "scale": z["left_dim"] ** -0.5,
             "mask": {"size": z["window"]},
-            "rot": {"base": 500000.0, "dims": z["left_dim"], "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 500000.0, "dims": z["left_dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     right = {"heads": z["state_heads"], "dim": z["state_dim"], "vdim": z["state_vdim"], "tau": z["tau"], "rank": z["rank"]}
     pair = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}
     ssm = {"heads": z["ssm_heads"], "vdim": z["ssm_vdim"], "state": z["ssm_state"], "groups": z["ssm_groups"], "conv": z["taps"],
@@ -1039,7 +1039,7 @@ def rarutar_folders(shape: str, layers: int):
                "max_positions": 16384}
     folders = []
     for tag, config in (("rarutar", raw), ("letanex", letanex)):
-        folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_rarutar_{shape}_{tag}_L{layers}"
+        folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_rarutar2_{shape}_{tag}_L{layers}"
         if not (folder / "complete").exists():
             print(f"[bench] writing random weights to {folder}", file=sys.stderr, flush=True)
             write_random_model(folder, parse_config(config), seed=0)
