@@ -34,18 +34,22 @@ class GroupSpec:
 
     kind ``full`` keeps all positions; ``window`` keeps the last ``window``
     positions that a query can still see (a query at position q sees keys
-    p with q - p < window).
+    p with q - p < window), and the sequence's first ``keep_first`` positions,
+    which every later query sees.
     """
     name: str
     kind: str = "full"
     window: int | None = None
     slots: tuple[int, ...] = ()
+    keep_first: int = 0
 
     def __post_init__(self):
         if self.kind not in ("full", "window"):
             raise CacheError(f"unknown cache group kind {self.kind!r}")
         if (self.kind == "window") != (self.window is not None) or (self.window is not None and self.window <= 0):
             raise CacheError("a window group needs a positive window, a full group none")
+        if self.keep_first < 0 or (self.keep_first and self.kind != "window"):
+            raise CacheError("only a window group keeps first positions")
 
 
 class PagePool:
@@ -247,7 +251,8 @@ class CacheManager:
             first_needed = seq.length - spec.window + 1
             whole_pages_before = max(0, first_needed) // self.page_tokens
             table = seq.tables[group]
-            for index in range(min(whole_pages_before, len(table))):
+            kept_pages = -(-spec.keep_first // self.page_tokens)       # pages that hold a kept first position stay
+            for index in range(kept_pages, min(whole_pages_before, len(table))):
                 if table[index] >= 0:
                     self.pools[group].release(table[index])
                     table[index] = -1

@@ -29,8 +29,9 @@ def plan_groups(model) -> tuple[list[GroupSpec], list[int]]:
         index = keys.index(spec.group_key)
         members[index].append(slot)
         slot_group.append(index)
-    groups = [GroupSpec(name=f"{kind}{window or ''}", kind=kind, window=window, slots=tuple(members[i]))
-              for i, (kind, window) in enumerate(keys)]
+    groups = [GroupSpec(name=f"{kind}{window or ''}" + (f"+{keep}" if keep else ""), kind=kind, window=window, slots=tuple(members[i]),
+                        keep_first=keep)
+              for i, (kind, window, keep) in enumerate(keys)]
     if not groups:
         groups = [GroupSpec(name="empty", kind="full", slots=())]
     return groups, slot_group
@@ -104,10 +105,11 @@ class CacheStorage:
         return CacheView(self.keys[slot], self.values[slot], ctx.block_tables[self.slot_group[slot]],
                          self.page_tokens, write)
 
-    def state_view(self, layer: int, ctx):
-        if self.states[layer] is None:
+    def state_view(self, entry: int, ctx):
+        """The state entry's buffer(s) with the step's slots; entries are those of ``model.state_specs()``."""
+        if self.states[entry] is None:
             return None
-        return StateView(self.states[layer], ctx.state_slots)
+        return StateView(self.states[entry], ctx.state_slots)
 
     def clear_state(self, slot: int) -> None:
         """Zero a state slot when a request takes it."""

@@ -48,11 +48,15 @@ class LayerCall:
     cache slots: the slot the layer's mixer reads, and writes when
     ``writes_cache``.  A layer may appear more than once in the order, and a
     call with ``writes_cache=False`` reads the cache that an earlier call
-    filled (another layer's cache).
+    filled (another layer's cache).  ``state`` names the per-request state
+    that the call's mixer carries: None is the layer's own (entry ``layer``);
+    a layer that runs several times with a state per run gives its further
+    calls entries from ``len(layers)`` on.
     """
     layer: int
     cache: int
     writes_cache: bool = True
+    state: int | None = None
 
 
 @dataclass(frozen=True)
@@ -77,6 +81,9 @@ class ModelSpec:
         slots = sorted({c.cache for c in self.order})
         if slots != list(range(len(slots))):
             raise ConfigError("cache slots of the run order must be 0..n-1 without gaps")
+        entries = sorted({c.layer if c.state is None else c.state for c in self.order})
+        if entries and (entries[0] < 0 or entries[-1] >= len(self.layers) + len(self.order)):
+            raise ConfigError("a layer call names a state entry out of range")
         written = set()
         for call in self.order:
             if call.writes_cache:

@@ -6,7 +6,11 @@
 //                  with S [dim, vdim] float32 in the request's state slot.  Two ways to make a_t and c_t:
 //                    per key channel (gated linear attention): a_t[i] = sigmoid(z_t[i] + bias[i])^(1/tau), c_t = 1;
 //                    per head (a selective state space):      dt = softplus(z_t[h] + bias[h]), a_t[i] = exp(-exp(a_log[h]) dt),
-//                                                             c_t = dt.
+//                                                             c_t = dt;
+//                    given (a matrix memory with exponential gates): a_t and c_t per head come ready-made from the
+//                                                             caller (`da`, `dc`), whatever the portion's length.
+//                  With `ones_col` the value row gets one more column that is always 1 (column `v_cols` of the state
+//                  and of the output): the state's extra column is then sum of the decayed c_t k_t, a normaliser.
 //                  q and k may be shared by the heads of a group (`groups` <= heads).  One block per (request, head,
 //                  block of value columns) with its part of the state in registers; the tokens' vectors come through
 //                  shared memory a few tokens at a time.  The order of operations per element is the tokens' order:
@@ -25,7 +29,7 @@ __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + lo
 __device__ __forceinline__ float silu_g(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_g(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-enum ScanDecay : int { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1 };
+enum ScanDecay : int { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1, DECAY_GIVEN = 2 };
 
 template <typename T>
 struct ScanParams {
@@ -47,6 +51,7 @@ struct ScanParams {
   float* sums;                         // [max_chunks, heads, dim, vdim]: a chunk's own sums, then the state before the chunk
   float* prods;                        // [max_chunks, heads, dim]: the product of a chunk's decays
   int chunk, requests;
+  int v_cols, ones_col;                // columns the value rows really have (<= vdim); column v_cols of the state is fed 1
 };
 
 // The chunks of all requests are numbered in the requests' order, ceil(tokens / chunk) each.  Finds chunk `index`:
@@ -112,7 +117,7 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
     return;
   }
   const int g = h / (p.heads / p.groups);
-  const bool per_head = p.mode == DECAY_PER_HEAD;
+  const bool per_head = p.mode != DECAY_PER_CHANNEL;
   float* mine = p.state + (((size_t)slot * p.heads + h) * dim) * p.vdim;
   // the chunk's place in the scratch: the blocks before it belong to the requests before r and to r's earlier chunks
   float* held = PHASE == SCAN_WHOLE ? nullptr : p.sums + (((size_t)(blockIdx.x) * p.heads + h) * dim) * p.vdim;
@@ -134,7 +139,7 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
     if (PHASE == SCAN_CHUNK_SUMS) P[j] = 1.f;
   }
   const float skip = p.skip ? p.skip[h] : 0.f;
-  const float rate = per_head ? expf(p.a_log[h]) : 0.f;
+  const float rate = p.mode == DECAY_PER_HEAD ? expf(p.a_log[h]) : 0.f;
   const int first = p.q_start[r] + chunk_at * (PHASE == SCAN_WHOLE ? 0 : p.chunk);
   const int last = PHASE == SCAN_WHOLE ? p.q_start[r + 1] : min(p.q_start[r + 1], first + p.chunk);
   auto z_at = [&](size_t index) { return p.z_f32 ? ((const float*)p.z)[index] : to_float(((const T*)p.z)[index]); };
@@ -146,7 +151,7 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
     const size_t tb = (size_t)t0;
     const T* qrow = p.q + tb * p.q_stride + (size_t)g * dim;
     const T* krow = p.k + tb * p.k_stride + (size_t)g * dim;
-    const T* vrow = p.v + tb * p.v_stride + (size_t)h * p.vdim;
+    const T* vrow = p.v + tb * p.v_stride + (size_t)h * p.v_cols;
     const float* arow = PHASE == SCAN_WHOLE ? nullptr : p.da + (per_head ? tb * p.heads + h : (tb * p.heads + h) * dim);
     const float* crow = (PHASE == SCAN_WHOLE || !per_head) ? nullptr : p.dc + tb * p.heads + h;
 #pragma unroll
@@ -169,7 +174,7 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
 #pragma unroll
     for (int u = 0; u < VPT; u++) {
       const int e = tid + u * SCAN_THREADS, tt = e >> cb_log2, column = blockIdx.z * cb + (e & (cb - 1));
-      rv[u] = (tt < n && column < p.vdim) ? to_float(vrow[tt * p.v_stride + column]) : 0.f;
+      rv[u] = (tt < n && column < p.v_cols) ? to_float(vrow[tt * p.v_stride + column]) : (p.ones_col && tt < n && column == p.v_cols) ? 1.f : 0.f;
     }
   };
   if (first < last) fetch(first);
@@ -455,6 +460,10 @@ int launch_scan_tiles(const ScanParams<T>& p, int requests, int max_chunks, cuda
   const size_t smem = (size_t)batch * ((size_t)ROWS * slices * sizeof(float4) + (size_t)cb * sizeof(float));
   const dim3 grid(requests, p.heads, (p.vdim + cb - 1) / cb);
   SPROUT_REQUIRE(grid.z <= 65535, "gated_scan: too many value columns");
+  if (p.sums == nullptr && p.mode == DECAY_GIVEN) {
+    sprout_launch(gated_scan_kernel<T, ROWS, COLS, SCAN_CHUNK_OUT>, grid, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
+    return sprout_check_launch("gated_scan");
+  }
   if (p.sums == nullptr) {
     sprout_launch(gated_scan_kernel<T, ROWS, COLS, SCAN_WHOLE>, grid, dim3(SCAN_THREADS), smem, stream, p, slices_log2, batch);
     return sprout_check_launch("gated_scan");
@@ -485,9 +494,16 @@ SPROUT_API int sprout_gated_scan(const void* q, int q_stride, const void* k, int
                                  float inv_tau, float q_scale, int mode, int requests, int heads, int groups, int dim, int vdim,
                                  const int* q_start, const int* state_slots, float* state, int num_slots, float* out, int* status,
                                  int tokens, int chunk, int max_chunks, float* da, float* dc, float* sums, float* prods,
-                                 cudaStream_t stream) {
-  SPROUT_REQUIRE(q && k && v && z && bias && q_start && state_slots && state && out && status, "gated_scan: null pointer");
-  if (sums) {
+                                 int v_cols, int ones_col, cudaStream_t stream) {
+  SPROUT_REQUIRE(q && k && v && q_start && state_slots && state && out && status, "gated_scan: null pointer");
+  SPROUT_REQUIRE(mode == DECAY_GIVEN ? (da && dc) : (z && bias), "gated_scan: the decay's inputs are missing");
+  SPROUT_REQUIRE(v_cols > 0 && v_cols <= vdim && (!ones_col || v_cols < vdim), "gated_scan: the value rows' columns do not fit the state's");
+  if (mode == DECAY_GIVEN && !sums) {
+    // one walk per request over ready-made decays: the outputs' walk of the chunked form with a chunk that holds any portion
+    chunk = 1 << 30;
+    max_chunks = requests;
+  }
+  if (sums && mode != DECAY_GIVEN) {
     // portions in chunks: scratch for the decays of every token and for every chunk's sums and decay product
     SPROUT_REQUIRE(chunk > 0 && max_chunks > 0 && tokens > 0 && da && prods && (mode != DECAY_PER_HEAD || dc),
                    "gated_scan: the chunked form needs its scratch");
@@ -499,19 +515,19 @@ SPROUT_API int sprout_gated_scan(const void* q, int q_stride, const void* k, int
   }
   SPROUT_REQUIRE(requests > 0 && heads > 0 && groups > 0 && heads % groups == 0 && dim > 0 && vdim > 0 && num_slots > 0,
                  "gated_scan: bad sizes");
-  SPROUT_REQUIRE(mode == DECAY_PER_CHANNEL || (mode == DECAY_PER_HEAD && a_log), "gated_scan: unknown decay form");
+  SPROUT_REQUIRE(mode == DECAY_PER_CHANNEL || (mode == DECAY_PER_HEAD && a_log) || mode == DECAY_GIVEN, "gated_scan: unknown decay form");
   SPROUT_REQUIRE(heads <= 65535, "gated_scan: too many heads");
   if (dtype == SPROUT_F32) {
     ScanParams<float> p{(const float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, z, z_stride, z_f32,
                         bias, a_log, skip, inv_tau, q_scale, mode, heads, groups, dim, vdim, q_start, state_slots, state,
-                        num_slots, out, status, da, dc, sums, prods, chunk, requests};
+                        num_slots, out, status, da, dc, sums, prods, chunk, requests, v_cols, ones_col};
     return launch_scan(p, requests, max_chunks, stream);
   }
   if (dtype == SPROUT_BF16) {
     ScanParams<__nv_bfloat16> p{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
                                 v_stride, z, z_stride, z_f32, bias, a_log, skip, inv_tau, q_scale, mode, heads,
                                 groups, dim, vdim, q_start, state_slots, state, num_slots, out, status, da, dc, sums, prods, chunk,
-                                requests};
+                                requests, v_cols, ones_col};
     return launch_scan(p, requests, max_chunks, stream);
   }
   return sprout_fail("gated_scan: unknown dtype %d", dtype);

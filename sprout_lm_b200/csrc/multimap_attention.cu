@@ -9,7 +9,11 @@
 // with `norm_eps` > 0, divided by its root mean square over vdim, and times `out_scale`.
 //
 //  * rope_maps_append:          rotates the first `rot` elements of every query and key vector by the
-//                               token's position (half-split pairs) and appends keys and values to the cache.
+//                               token's position (half-split pairs) and appends keys and values to the cache; before
+//                               the rotation it can divide every vector by its root mean square and multiply it by a
+//                               weight (one for queries, one for keys).
+// Options of both attention kernels: a mask (a window, a window that also keeps the first positions, chunks), a cap on
+// the scaled scores (cap * tanh(score / cap)), a sink per head in the softmax denominator, a gate per head.
 //  * multimap_attention_simple: one block per (token, query head); keys in chunks of 128 aligned to
 //                               absolute position with running maxima and sums: what is done for a query
 //                               does not depend on how the tokens were cut into steps.
@@ -42,6 +46,7 @@ rope_maps_append_kernel(T* __restrict__ rows, int row_stride, const int* __restr
                         const float* __restrict__ cos_table, const float* __restrict__ sin_table, int max_positions,
                         T* __restrict__ k_cache, T* __restrict__ v_cache, int q_vectors, int kv_heads, int maps, int dim,
                         int rot, int vdim, int page_tokens, int num_pages, int write, float unit_eps, int value_from_key,
+                        const float* __restrict__ q_weight, const float* __restrict__ k_weight, float weight_eps,
                         int* status) {
   pdl_launch_dependents();
   pdl_wait();
@@ -66,9 +71,21 @@ rope_maps_append_kernel(T* __restrict__ rows, int row_stride, const int* __restr
   for (int vec = warp; vec < vectors; vec += warps) {
     const bool is_key = vec >= q_vectors;
     if (is_key && page < 0) continue;
-    if (!is_key && !turn && unit_eps <= 0.f) continue;          // nothing to do to this query vector
+    const float* weight = is_key ? k_weight : q_weight;           // the norm before the rotation, when the vector has one
+    if (!is_key && !turn && unit_eps <= 0.f && weight == nullptr) continue;   // nothing to do to this query vector
     T* src = row + (size_t)vec * dim;                             // the key vectors follow the query vectors
     float vals[ROPE_MAX_PER_LANE], raw[ROPE_MAX_PER_LANE];
+    float before = 1.0f;
+    if (weight != nullptr) {
+      float sq = 0.f;
+#pragma unroll
+      for (int j = 0; j < ROPE_MAX_PER_LANE; j++)
+        if (lane + 32 * j < dim) {
+          const float x = to_float(src[lane + 32 * j]);
+          sq = fmaf(x, x, sq);
+        }
+      before = 1.0f / sqrtf(warp_sum(sq) / (float)dim + weight_eps);
+    }
     float squares = 0.f;
 #pragma unroll
     for (int j = 0; j < ROPE_MAX_PER_LANE; j++) {
@@ -77,9 +94,11 @@ rope_maps_append_kernel(T* __restrict__ rows, int row_stride, const int* __restr
       if (d < dim) {
         float x = to_float(src[d]);
         raw[j] = x;
+        if (weight != nullptr) x = x * before * weight[d];
         if (turn && d < rot) {
-          const int i = d < half ? d : d - half;
-          const float other = to_float(src[d < half ? d + half : d - half]);
+          const int i = d < half ? d : d - half, partner = d < half ? d + half : d - half;
+          float other = to_float(src[partner]);
+          if (weight != nullptr) other = other * before * weight[partner];
           x = d < half ? x * cs[i] - other * sn[i] : x * cs[i] + other * sn[i];
         }
         vals[j] = x;
@@ -116,7 +135,13 @@ rope_maps_append_kernel(T* __restrict__ rows, int row_stride, const int* __restr
 
 // The first position that a query at `pos` sees: 0 (causal), pos - size + 1 (a window of `size` positions, itself
 // included) or the start of its chunk of `size` positions counted from position 0.
+// `keep` (a window only): the first `keep` positions stay visible to every later query, at their own positions.
 enum MaskKind : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_CHUNK = 2 };
+// cap * tanh(s / cap) for the bfloat16 kernel: through one exponential, absolute error about cap * 2e-7
+__device__ __forceinline__ float soft_cap_fast(float s, float cap, float inv_cap) {
+  const float e = __expf(2.0f * s * inv_cap);
+  return cap * (1.0f - __fdividef(2.0f, e + 1.0f));
+}
 __device__ __forceinline__ int first_visible(int kind, int size, int pos) {
   if (kind == MASK_WINDOW) return max(0, pos - size + 1);
   if (kind == MASK_CHUNK) return pos < 0 ? 0 : (pos / size) * size;
@@ -130,8 +155,8 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
                                  const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                  T* __restrict__ out, int out_stride, int heads, int kv_heads, int dim, int vdim,
                                  int page_tokens, int num_pages, float scale, float lambda, float norm_eps,
-                                 float out_scale, int mask_kind, int mask_size, const float* __restrict__ sink,
-                                 const T* __restrict__ gate, int gate_stride, int* status) {
+                                 float out_scale, int mask_kind, int mask_size, int mask_keep, float softcap,
+                                 const float* __restrict__ sink, const T* __restrict__ gate, int gate_stride, int* status) {
   extern __shared__ float smem[];
   float* qs = smem;                                   // MAPS * dim
   float* probs = qs + MAPS * dim;                     // MAPS * CHUNK
@@ -157,9 +182,11 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
     for (int part = 0; part < PARTS; part++) acc[m][part] = 0.f;
   }
   const int lo = first_visible(mask_kind, mask_size, pos);
-  for (int base = (lo / CHUNK) * CHUNK; base <= pos; base += CHUNK) {
+  const int keep = min(mask_keep, lo);                // kept first positions that the window itself does not reach
+  for (int base = 0; base <= pos; base += CHUNK) {
+    if (base >= keep && base + CHUNK <= lo) continue; // a chunk of which the query sees nothing
     const int p = base + tid;
-    bool valid = p >= lo && p <= pos;
+    bool valid = (p >= lo || p < keep) && p <= pos;
     long long index = -1;
     if (valid) {
       const int page = table[p / page_tokens];
@@ -179,6 +206,7 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
         float dot = 0.f;
         for (int d = 0; d < dim; d++) dot = fmaf(qs[m * dim + d], to_float(key[d]), dot);
         s[m] = dot * scale;
+        if (softcap > 0.f) s[m] = softcap * tanhf(s[m] / softcap);
       }
     }
     row_index[tid] = index;
@@ -260,7 +288,12 @@ struct MultiMapParams {
   // what a query sees (MaskKind and its size), an optional term exp(sink[head]) in every softmax denominator, and an
   // optional gate: the head's output times sigmoid(gate[token * gate_stride + head])
   int mask_kind, mask_size; const float* sink; const __nv_bfloat16* gate; int gate_stride;
+  // a window's kept first positions, and the cap on the scaled scores (0: none)
+  int mask_keep; float softcap;
 };
+
+// What the running maxima are multiplied by on their way into the exponentials: capped scores are already scaled.
+__device__ __forceinline__ float score_scale(const MultiMapParams& p) { return p.softcap > 0.f ? 1.0f : p.scale; }
 
 template <int DIM, int VDIM, int MAPS, bool SPLIT>
 __global__ void __launch_bounds__(MM_THREADS)
@@ -307,6 +340,10 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   const int kv_tiles = max_limit / MM_KEYS + 1;
   const int min_lo = s_lo[0];                                       // the first key any row sees: lo grows with the position
   const int tile_lo = min_lo / MM_KEYS;
+  // the CTA's tiles: those of the kept first positions that lie before the window's, then the window's up to the last query
+  const int keep_tiles = min((p.mask_keep + MM_KEYS - 1) / MM_KEYS, tile_lo);
+  const int list_tiles = keep_tiles + (kv_tiles - tile_lo);
+  auto tile_of = [&](int i) { return i < keep_tiles ? i : tile_lo + (i - keep_tiles); };
 
   for (int idx = tid; idx < MM_ROWS * KCHUNKS; idx += MM_THREADS) {
     const int row = idx / KCHUNKS, c = idx % KCHUNKS;
@@ -318,7 +355,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
     if (tid < MM_KEYS) {
       const int key = t * MM_KEYS + tid;
       long long row = -1;
-      if (key >= min_lo && key <= max_limit) {
+      if ((key >= min_lo || key < p.mask_keep) && key <= max_limit) {
         const int page = table[key / p.page_tokens];
         if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
         else row = ((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens;
@@ -342,10 +379,10 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
       else *(uint4*)dst = make_uint4(0, 0, 0, 0);
     }
   };
-  const int first_tile = tile_lo + (SPLIT ? (int)blockIdx.z : 0), tile_step = SPLIT ? p.ksplit : 1;    // this CTA's tiles: every tile_step-th
-  if (first_tile < kv_tiles) find_rows(first_tile, 0);
+  const int first_tile = SPLIT ? (int)blockIdx.z : 0, tile_step = SPLIT ? p.ksplit : 1;    // this CTA's tiles: every tile_step-th of the list
+  if (first_tile < list_tiles) find_rows(tile_of(first_tile), 0);
   __syncthreads();
-  if (first_tile < kv_tiles) load_tile(0);
+  if (first_tile < list_tiles) load_tile(0);
   cp_async_commit();
 
   // SPLIT (a step in which no request has more than 16 rows: single tokens, the heads of one key/value group): a CTA
@@ -367,23 +404,25 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
 #pragma unroll
     for (int i = 0; i < VDIM / 8; i++) o[m][i][0] = o[m][i][1] = o[m][i][2] = o[m][i][3] = 0.f;
   }
-  const float scale_log2 = p.scale * 1.4426950408889634f;
+  const float scale_log2 = score_scale(p) * 1.4426950408889634f;
+  const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
   const int warp_min_limit = s_limit[min(qrow, last_row)];
   const int warp_min_lo = s_lo[min(qrow, last_row)], warp_max_lo = s_lo[min(qrow + 15, last_row)];
 
   int buf = 1;
-  for (int t = first_tile; t < kv_tiles; t += tile_step) {
+  for (int ti = first_tile; ti < list_tiles; ti += tile_step) {
+    const int t = tile_of(ti);
     buf ^= 1;
-    if (t + tile_step < kv_tiles) find_rows(t + tile_step, buf ^ 1);
+    if (ti + tile_step < list_tiles) find_rows(tile_of(ti + tile_step), buf ^ 1);
     __syncthreads();                                   // rows visible; everyone is done with buffer buf ^ 1
-    if (t + tile_step < kv_tiles) load_tile(buf ^ 1);
+    if (ti + tile_step < list_tiles) load_tile(buf ^ 1);
     cp_async_commit();
     cp_async_wait<1>();                                // tile t (and Q) have landed
     __syncthreads();
     const __nv_bfloat16* tK = sK + buf * MM_KEYS * KSTRIDE;
     const __nv_bfloat16* tV = sV + buf * MM_KEYS * VSTRIDE;
     const int kv0 = t * MM_KEYS;
-    if (kv0 + kb > s_limit[min(qrow + 15, last_row)] || kv0 + kb + nk * 16 <= warp_min_lo) continue;   // no row of this warp sees its keys of the tile
+    if (kv0 + kb > s_limit[min(qrow + 15, last_row)] || (kv0 + kb + nk * 16 <= warp_min_lo && kv0 + kb >= p.mask_keep)) continue;   // no row of this warp sees its keys of the tile
 #pragma unroll
     for (int m = 0; m < MAPS; m++) {
       float s[MM_KEYS / 8][4];
@@ -400,6 +439,15 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
           ldmatrix_x4(b, tK + (kb + n2 * 16 + (lane & 7) + (lane >> 4) * 8) * KSTRIDE + m * DIM + kk * 16 + ((lane >> 3) & 1) * 8);
           mma_bf16(s[2 * n2], a, b[0], b[1]);
           mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+      if (p.softcap > 0.f) {
+        const float cap = p.softcap, pre = p.scale;
+#pragma unroll
+        for (int i = 0; i < MM_KEYS / 8; i++) {
+          if (i >= 2 * nk) break;
+#pragma unroll
+          for (int c = 0; c < 4; c++) s[i][c] = soft_cap_fast(s[i][c] * pre, cap, inv_cap);
         }
       }
       float t_max0 = -INFINITY, t_max1 = -INFINITY;
@@ -419,10 +467,11 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
         for (int i = 0; i < MM_KEYS / 8; i++) {
           if (i >= 2 * nk) break;
           const int key = kv0 + kb + i * 8 + qc * 2;
-          if (key < lo0) s[i][0] = -INFINITY;
-          if (key + 1 < lo0) s[i][1] = -INFINITY;
-          if (key < lo1) s[i][2] = -INFINITY;
-          if (key + 1 < lo1) s[i][3] = -INFINITY;
+          const int kept = p.mask_keep;
+          if (key < lo0 && key >= kept) s[i][0] = -INFINITY;
+          if (key + 1 < lo0 && key + 1 >= kept) s[i][1] = -INFINITY;
+          if (key < lo1 && key >= kept) s[i][2] = -INFINITY;
+          if (key + 1 < lo1 && key + 1 >= kept) s[i][3] = -INFINITY;
         }
       }
 #pragma unroll
@@ -609,7 +658,7 @@ multimap_merge_kernel(const MultiMapParams p, int vdim) {
   const int q0 = p.q_start[r], rows_total = (p.q_start[r + 1] - q0) * group;
   if (row >= rows_total) return;
   const int token = q0 + row / group, head = g * group + row % group;
-  const float scale_log2 = p.scale * 1.4426950408889634f;
+  const float scale_log2 = score_scale(p) * 1.4426950408889634f;
   const float* base = p.partial + (((size_t)r * p.kv_heads + g) * p.ksplit * 16 + row) * MAPS * (2 + vdim);
   const size_t share = (size_t)16 * MAPS * (2 + vdim);
   float v[2] = {0.f, 0.f};                             // columns threadIdx.x and threadIdx.x + 128
@@ -691,7 +740,8 @@ SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const 
                                              int max_q_len, int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
                                              int num_pages, float scale, float lambda, float norm_eps, float out_scale,
                                              int ksplit, float* partial, int mask_kind, int mask_size, const float* sink,
-                                             const void* gate, int gate_stride, int* status, cudaStream_t stream) {
+                                             const void* gate, int gate_stride, int mask_keep, float softcap, int* status,
+                                             cudaStream_t stream) {
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && q_start && positions && out && status, "multimap_attention_mma: null pointer");
   SPROUT_REQUIRE(requests > 0 && tiles > 0 && max_q_len > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 &&
                  num_pages > 0, "multimap_attention_mma: bad sizes");
@@ -702,9 +752,11 @@ SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const 
   MultiMapParams p{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
                    table_stride, q_start, positions, (__nv_bfloat16*)out, out_stride, requests, heads, kv_heads, page_tokens,
                    num_pages, scale, lambda, norm_eps, out_scale, status, ksplit, partial, mask_kind, mask_size, sink,
-                   (const __nv_bfloat16*)gate, gate_stride};
+                   (const __nv_bfloat16*)gate, gate_stride, mask_keep, softcap};
   SPROUT_REQUIRE(mask_kind == MASK_CAUSAL || ((mask_kind == MASK_WINDOW || mask_kind == MASK_CHUNK) && mask_size > 0),
                  "multimap_attention_mma: a window or a chunk needs a positive size");
+  SPROUT_REQUIRE(mask_keep >= 0 && (mask_keep == 0 || mask_kind == MASK_WINDOW) && softcap >= 0.f,
+                 "multimap_attention_mma: only a window keeps first positions; the cap is not negative");
   SPROUT_REQUIRE(!gate || gate_stride >= heads, "multimap_attention_mma: gate rows hold a number per head");
   SPROUT_REQUIRE(ksplit >= 1 && ksplit <= 64 && (ksplit == 1 || (partial && max_q_len * (heads / kv_heads) <= 16)),
                  "multimap_attention_mma: keys are divided among CTAs in single-token steps only, with scratch for the shares");
@@ -723,8 +775,8 @@ SPROUT_API int sprout_rope_maps_append(void* rows, int row_stride, int dtype, co
                                        const int* block_table, int table_stride, const float* cos_table,
                                        const float* sin_table, int max_positions, void* k_cache, void* v_cache, int tokens,
                                        int q_vectors, int kv_heads, int maps, int dim, int rot, int vdim, int page_tokens,
-                                       int num_pages, int write, float unit_eps, int value_from_key, int* status,
-                                       cudaStream_t stream) {
+                                       int num_pages, int write, float unit_eps, int value_from_key, const float* q_weight,
+                                       const float* k_weight, float weight_eps, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(rows && positions && status && tokens > 0 && q_vectors > 0 && dim > 0 && maps > 0, "rope_maps_append: bad arguments");
   SPROUT_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dim, "rope_maps_append: the rotated width must be even and at most dim");
   SPROUT_REQUIRE(rot == 0 || (cos_table && sin_table && max_positions > 0), "rope_maps_append: tables are missing");
@@ -732,18 +784,19 @@ SPROUT_API int sprout_rope_maps_append(void* rows, int row_stride, int dtype, co
                             num_pages > 0), "rope_maps_append: the cache is missing");
   SPROUT_REQUIRE(dim <= 32 * ROPE_MAX_PER_LANE, "rope_maps_append: vectors of up to %d elements (got %d)", 32 * ROPE_MAX_PER_LANE, dim);
   SPROUT_REQUIRE(!value_from_key || vdim == maps * dim, "rope_maps_append: values that are the keys have the keys' width");
+  SPROUT_REQUIRE((!q_weight && !k_weight) || weight_eps > 0.f, "rope_maps_append: a norm before the rotation needs a positive eps");
   const int need = q_vectors * dim + (write ? kv_heads * (maps * dim + (value_from_key ? 0 : vdim)) : 0);
   SPROUT_REQUIRE(row_stride >= need, "rope_maps_append: rows of %d elements, %d needed", row_stride, need);
   if (dtype == SPROUT_F32)
     sprout_launch(rope_maps_append_kernel<float>, dim3(tokens), dim3(128), 0, stream, (float*)rows, row_stride, positions,
                   seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions, (float*)k_cache,
                   (float*)v_cache, q_vectors, kv_heads, maps, dim, rot, vdim, page_tokens, num_pages, write, unit_eps,
-                  value_from_key, status);
+                  value_from_key, q_weight, k_weight, weight_eps, status);
   else if (dtype == SPROUT_BF16)
     sprout_launch(rope_maps_append_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, (__nv_bfloat16*)rows, row_stride,
                   positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
                   (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, q_vectors, kv_heads, maps, dim, rot, vdim, page_tokens,
-                  num_pages, write, unit_eps, value_from_key, status);
+                  num_pages, write, unit_eps, value_from_key, q_weight, k_weight, weight_eps, status);
   else
     return sprout_fail("rope_maps_append: unknown dtype %d", dtype);
   return sprout_check_launch("rope_maps_append");
@@ -755,7 +808,8 @@ SPROUT_API int sprout_multimap_attention_simple(const void* q, int q_stride, con
                                                 int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
                                                 int num_pages, float scale, float lambda, float norm_eps, float out_scale,
                                                 int mask_kind, int mask_size, const float* sink, const void* gate,
-                                                int gate_stride, int* status, cudaStream_t stream) {
+                                                int gate_stride, int mask_keep, float softcap, int* status,
+                                                cudaStream_t stream) {
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && seq_of_token && positions && out && status, "multimap_attention: null pointer");
   SPROUT_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 && num_pages > 0,
                  "multimap_attention: bad sizes");
@@ -765,6 +819,8 @@ SPROUT_API int sprout_multimap_attention_simple(const void* q, int q_stride, con
   SPROUT_REQUIRE(mask_kind == MASK_CAUSAL || ((mask_kind == MASK_WINDOW || mask_kind == MASK_CHUNK) && mask_size > 0),
                  "multimap_attention: a window or a chunk needs a positive size");
   SPROUT_REQUIRE(!gate || gate_stride >= heads, "multimap_attention: gate rows hold a number per head");
+  SPROUT_REQUIRE(mask_keep >= 0 && (mask_keep == 0 || mask_kind == MASK_WINDOW) && softcap >= 0.f,
+                 "multimap_attention: only a window keeps first positions; the cap is not negative");
   const size_t smem = (size_t)(maps * dim + maps * CHUNK + 36) * sizeof(float) + CHUNK * sizeof(long long);
   SPROUT_REQUIRE(smem <= 48 * 1024, "multimap_attention: key vectors too long (%d)", dim);
   dim3 grid(tokens, heads);
@@ -772,7 +828,7 @@ SPROUT_API int sprout_multimap_attention_simple(const void* q, int q_stride, con
   sprout_launch(multimap_attention_simple_kernel<T, M>, grid, dim3(CHUNK), smem, stream, (const T*)q, q_stride,           \
                 (const T*)k_cache, (const T*)v_cache, block_table, table_stride, seq_of_token, positions, (T*)out,        \
                 out_stride, heads, kv_heads, dim, vdim, page_tokens, num_pages, scale, lambda, norm_eps, out_scale,    \
-                mask_kind, mask_size, sink, (const T*)gate, gate_stride, status)
+                mask_kind, mask_size, mask_keep, softcap, sink, (const T*)gate, gate_stride, status)
   if (dtype == SPROUT_F32) {
     if (maps == 1) LAUNCH(float, 1); else LAUNCH(float, 2);
   } else if (dtype == SPROUT_BF16) {

@@ -4,13 +4,17 @@
 //                  choice = s + correction; the `top` largest choices (lowest index first among equals) are
 //                  taken; weight = s / (sum of the taken s + 1e-20) * scale.  Router outputs from
 //                  `experts` on are identity experts (their output is the token's h).  Counts the rows
-//                  of each real expert.
+//                  of each real expert.  Options: the outputs form `group_count` equal groups of neighbours, a group's
+//                  score is its largest s, and only outputs of the `group_keep` best groups can be taken; weights that
+//                  are the scores themselves (not renormalised); `extra` further rows of the router matrix whose
+//                  products are handed out as they are (a gate beside the router, in the same 32-bit product).
 //  * moe_arrange:  offsets of the experts' row ranges, every taken (token, place) of a real expert put
 //                  into its expert's range (`sorted`), and where it went (`place_of`).
 //  * moe_up / moe_down (plain): the experts' two products on CUDA cores over the arranged rows, every
 //                  output element summed in ascending k by one warp: act = f(W_gate a, W_up a),
 //                  rows = W_down act, f(g, u) = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
-//                  u' = clamp(u, -limit, limit).
+//                  u' = clamp(u, -limit, limit); or, for experts without a gate, act = gelu(W_up a) (the exact, erf form)
+//                  with a matrix of ff rows per expert.
 //  * moe_up / moe_down (mma):   the same two products on tensor cores (bfloat16, `mma.sync.m16n8k16`, float32
 //                  accumulation): a CTA makes 128 arranged rows of one expert x 128 columns, K in steps of 64
 //                  through a three-stage cp.async ring; the tile list follows the experts' row counts on the
@@ -35,8 +39,10 @@ template <typename T, int ROUTE_TOKENS>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ router, const float* __restrict__ correction,
                  int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int tokens, int width,
-                 int outputs, int experts, int top, float scale) {
+                 int softmax_outputs, int experts, int top, float scale, int extra, float* __restrict__ extra_out,
+                 int group_count, int group_keep, int renormalize) {
   extern __shared__ float smem[];
+  int outputs = softmax_outputs + extra;              // rows of the router matrix
   float* zs = smem;                                   // ROUTE_TOKENS x outputs: scores
   float* choices = zs + ROUTE_TOKENS * outputs;       // ROUTE_TOKENS x outputs
   float* rows = choices + ROUTE_TOKENS * outputs;     // ROUTE_TOKENS x width: the tokens' h as float32
@@ -70,6 +76,8 @@ moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict_
   const int t = t0 + warp;
   float* z = zs + warp * outputs;
   float* choice = choices + warp * outputs;
+  for (int e = lane; e < extra; e += 32) extra_out[(size_t)t * extra + e] = z[softmax_outputs + e];
+  outputs = softmax_outputs;                          // from here on: what the softmax is over
   float top_z = -INFINITY;
   for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, z[e]);
   top_z = warp_max(top_z);
@@ -80,9 +88,46 @@ moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict_
   for (int e = lane; e < outputs; e += 32) {
     const float s = expf(z[e] - top_z) / sum;
     z[e] = s;
-    choice[e] = s + correction[e];
+    choice[e] = s + (correction ? correction[e] : 0.f);
   }
   __syncwarp();
+  if (group_count > 1 && group_keep < group_count) {
+    // a group's score is its largest s; outputs outside the `group_keep` best groups (lowest index among equals) cannot
+    // be taken.  A kept group is marked in its first output's choice.
+    const int size = outputs / group_count;
+    for (int kept = 0; kept < group_keep; kept++) {
+      float best_s = -INFINITY;
+      int best = 0x7fffffff;
+      for (int g = lane; g < group_count; g += 32) {
+        if (choice[g * size] == INFINITY) continue;          // already kept
+        float top_s = -INFINITY;
+        for (int e = g * size; e < (g + 1) * size; e++) top_s = fmaxf(top_s, z[e]);
+        if (top_s > best_s) {
+          best_s = top_s;
+          best = g;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float other_s = __shfl_xor_sync(0xffffffffu, best_s, o);
+        const int other = __shfl_xor_sync(0xffffffffu, best, o);
+        if (other_s > best_s || (other_s == best_s && other < best)) {
+          best_s = other_s;
+          best = other;
+        }
+      }
+      if (best >= group_count) break;
+      __syncwarp();
+      if (lane == 0) choice[best * size] = INFINITY;
+      __syncwarp();
+    }
+    for (int g = lane; g < group_count; g += 32) {
+      const bool kept = choice[g * size] == INFINITY;
+      for (int e = g * size; e < (g + 1) * size; e++)
+        choice[e] = kept ? z[e] + (correction ? correction[e] : 0.f) : -INFINITY;
+    }
+    __syncwarp();
+  }
   // the largest choice `top` times; among equals the lowest index
   float taken = 0.f;
   for (int place = 0; place < top; place++) {
@@ -112,7 +157,7 @@ moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict_
     }
     __syncwarp();
   }
-  const float norm = scale / (taken + 1e-20f);
+  const float norm = renormalize ? scale / (taken + 1e-20f) : scale;
   __syncwarp();
   for (int place = lane; place < top; place += 32) weights[(size_t)t * top + place] *= norm;
 }
@@ -156,7 +201,9 @@ __device__ __forceinline__ int expert_of(const int* offsets, int experts, int ro
   return lo;
 }
 
+// `limit` <= 0 names an expert without a gate: the exact gelu of its one product.
 __device__ __forceinline__ float glu(float g, float u, float limit, float alpha) {
+  if (limit <= 0.f) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
@@ -179,14 +226,15 @@ moe_up_plain_kernel(const T* __restrict__ h, int h_stride, const int* __restrict
   for (int k = threadIdx.x; k < width; k += blockDim.x) a[k] = to_float(src[k]);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const T* w = w_gate_up + (size_t)e * 2 * ff * width;
+  const bool gated = limit > 0.f;                      // else the matrix has ff rows per expert and no up rows
+  const T* w = w_gate_up + (size_t)e * (gated ? 2 : 1) * ff * width;
   for (int j = blockIdx.y * 8 + warp; j < ff; j += gridDim.y * 8) {
     const T* wg = w + (size_t)j * width;
-    const T* wu = w + (size_t)(ff + j) * width;
+    const T* wu = w + (size_t)((gated ? ff : 0) + j) * width;
     float g = 0.f, u = 0.f;
     for (int k = lane; k < width; k += 32) {
       g = fmaf(a[k], to_float(wg[k]), g);
-      u = fmaf(a[k], to_float(wu[k]), u);
+      if (gated) u = fmaf(a[k], to_float(wu[k]), u);
     }
     g = warp_sum(g);
     u = warp_sum(u);
@@ -242,7 +290,9 @@ __device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t
 
 // UP: A rows are h[order[row] / top], B = w[expert] of [2 ff, K] (gate rows, then up rows), out = act [rows, ff] bfloat16.
 // else: A rows are act[row] of [rows, K], B = w[expert] of [N, K], out = rows_out [rows, N] float32.
-template <bool UP>
+// KIND 0: the down product; 1: the gated up product (UP); 2: the up product of experts without a gate: A rows gathered
+// like UP, B = w[expert] of [N, K], out = act [rows, N] bfloat16 = gelu(product), the exact form.
+template <int KIND>
 __global__ void __launch_bounds__(GTHREADS)
 moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int* __restrict__ order,
                     const int* __restrict__ offsets, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
@@ -252,6 +302,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int
   __shared__ const __nv_bfloat16* a_rows[GM];
   pdl_launch_dependents();
   pdl_wait();
+  constexpr bool UP = KIND == 1, GATHER = KIND != 0;
   int expert, row0, row_end;
   if (!find_tile(offsets, experts, blockIdx.x, expert, row0, row_end)) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp & 3, wn = warp >> 2;
@@ -260,7 +311,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int
   const __nv_bfloat16* wexp = w + (size_t)expert * (UP ? 2 * N : N) * K;
   if (tid < GM) {
     const int row = row0 + tid;
-    a_rows[tid] = row < row_end ? (UP ? a + (size_t)(order[row] / top) * a_stride : a + (size_t)row * a_stride) : nullptr;
+    a_rows[tid] = row < row_end ? (GATHER ? a + (size_t)(order[row] / top) * a_stride : a + (size_t)row * a_stride) : nullptr;
   }
   __syncthreads();
   auto As = [&](int stage) { return (Tile)(gemm_smem + (size_t)stage * (GM + GN) * GSTRIDE * sizeof(__nv_bfloat16)); };
@@ -349,6 +400,17 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int
           }
           *(__nv_bfloat162*)(dst + j) = __floats2bfloat162_rn(v[0], v[1]);
         }
+      } else if (KIND == 2) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * N;
+#pragma unroll
+        for (int ni = 0; ni < 8; ni++) {
+          const int n = n0 + wn * 64 + ni * 8 + qc * 2;
+          if (n >= N) continue;
+          // rounded to bfloat16 before the activation, as a separate product would leave it
+          const float g0 = __bfloat162float(__float2bfloat16_rn(acc[mi][ni][half * 2]));
+          const float g1 = __bfloat162float(__float2bfloat16_rn(acc[mi][ni][half * 2 + 1]));
+          *(__nv_bfloat162*)(dst + n) = __floats2bfloat162_rn(glu(g0, 0.f, 0.f, 0.f), glu(g1, 0.f, 0.f, 0.f));
+        }
       } else {
         float* dst = (float*)out + (size_t)row * N;
 #pragma unroll
@@ -384,7 +446,8 @@ moe_few_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int* __r
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const __nv_bfloat16* wexp = w + (size_t)e * (UP ? 2 * N : N) * K;
+  const bool gated = UP && limit > 0.f;               // else one matrix row per output
+  const __nv_bfloat16* wexp = w + (size_t)e * (gated ? 2 * N : N) * K;
   for (int j = blockIdx.y * FEW_COLS + warp; j < min(N, (blockIdx.y + 1) * FEW_COLS); j += 8) {
     const __nv_bfloat16* w0 = wexp + (size_t)j * K;
     const __nv_bfloat16* w1 = wexp + (size_t)(N + j) * K;     // UP: the up row that goes with gate row j
@@ -394,7 +457,7 @@ moe_few_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int* __r
     for (int c = lane; c < chunks; c += 32) {
       const uint4 g = *(const uint4*)(w0 + c * 8);
       uint4 u = make_uint4(0, 0, 0, 0);
-      if (UP) u = *(const uint4*)(w1 + c * 8);
+      if (gated) u = *(const uint4*)(w1 + c * 8);
       const __nv_bfloat162* gp = (const __nv_bfloat162*)&g;
       const __nv_bfloat162* up = (const __nv_bfloat162*)&u;
 #pragma unroll
@@ -407,7 +470,7 @@ moe_few_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int* __r
           const float2 xv = __bfloat1622float2(xp[i]), gv = __bfloat1622float2(gp[i]);
           s0[r] = fmaf(xv.x, gv.x, s0[r]);
           s0[r] = fmaf(xv.y, gv.y, s0[r]);
-          if (UP) {
+          if (gated) {
             const float2 uv = __bfloat1622float2(up[i]);
             s1[r] = fmaf(xv.x, uv.x, s1[r]);
             s1[r] = fmaf(xv.y, uv.y, s1[r]);
@@ -420,7 +483,7 @@ moe_few_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int* __r
       if (r >= count) break;
       const float g = warp_sum(s0[r]);
       if (UP) {
-        const float u = warp_sum(s1[r]);
+        const float u = gated ? warp_sum(s1[r]) : 0.f;
         if (lane == 0)
           ((__nv_bfloat16*)out)[(size_t)(row0 + r) * N + j] = __float2bfloat16_rn(
               glu(__bfloat162float(__float2bfloat16_rn(g)), __bfloat162float(__float2bfloat16_rn(u)), limit, alpha));
@@ -481,14 +544,23 @@ moe_combine_vec_kernel(float* __restrict__ y, const T* __restrict__ h, int h_str
 
 }  // namespace
 
+// `outputs`: what the softmax is over; the router matrix has `outputs + extra` rows, and extra_out [tokens, extra] gets the
+// last rows' products.  `correction` may be null (none).
 SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const float* router, const float* correction, int* ids,
                                 float* weights, int* counts, int tokens, int width, int outputs, int experts, int top,
-                                float scale, cudaStream_t stream) {
-  SPROUT_REQUIRE(h && router && correction && ids && weights && counts, "moe_route: null pointer");
+                                float scale, int extra, float* extra_out, int group_count, int group_keep, int renormalize,
+                                cudaStream_t stream) {
+  SPROUT_REQUIRE(h && router && ids && weights && counts, "moe_route: null pointer");
+  SPROUT_REQUIRE(extra >= 0 && (extra == 0 || extra_out), "moe_route: the extra rows' products need a place");
+  SPROUT_REQUIRE(group_count >= 1 && group_keep >= 1 && group_keep <= group_count && outputs % group_count == 0,
+                 "moe_route: %d outputs do not form %d equal groups of which %d are kept", outputs, group_count, group_keep);
+  SPROUT_REQUIRE(group_keep == group_count || top <= group_keep * (outputs / group_count),
+                 "moe_route: the kept groups hold fewer outputs than are taken");
   SPROUT_REQUIRE(tokens > 0 && width > 0 && outputs > 0 && experts >= 0 && experts <= outputs && top > 0 && top <= outputs,
                  "moe_route: bad sizes (outputs %d, experts %d, top %d)", outputs, experts, top);
-  const int per_block = tokens > 64 && (size_t)8 * (2 * outputs + width) * sizeof(float) <= 200 * 1024 ? 8 : 1;
-  const size_t smem = (size_t)per_block * (2 * outputs + width) * sizeof(float);
+  const int rows_of_router = outputs + extra;
+  const int per_block = tokens > 64 && (size_t)8 * (2 * rows_of_router + width) * sizeof(float) <= 200 * 1024 ? 8 : 1;
+  const size_t smem = (size_t)per_block * (2 * rows_of_router + width) * sizeof(float);
   SPROUT_REQUIRE(smem <= 200 * 1024, "moe_route: too many router outputs (%d) or too wide rows (%d)", outputs, width);
   static bool prepared = false;
   if (!prepared) {
@@ -501,7 +573,7 @@ SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const fl
   dim3 grid((tokens + per_block - 1) / per_block);
 #define ROUTE(T, N)                                                                                                    \
   sprout_launch(moe_route_kernel<T, N>, grid, dim3(ROUTE_THREADS), smem, stream, (const T*)h, h_stride, router, correction, ids, \
-                weights, counts, tokens, width, outputs, experts, top, scale)
+                weights, counts, tokens, width, outputs, experts, top, scale, extra, extra_out, group_count, group_keep, renormalize)
   if (dtype == SPROUT_F32) {
     if (per_block == 1) ROUTE(float, 1); else ROUTE(float, 8);
   } else if (dtype == SPROUT_BF16) {
@@ -590,16 +662,22 @@ SPROUT_API int sprout_moe_experts_mma(const void* h, int h_stride, const int* or
   }
   static bool prepared = false;
   if (!prepared) {
-    cudaFuncSetAttribute(moe_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    cudaFuncSetAttribute(moe_gemm_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(moe_gemm_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(moe_gemm_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(moe_gemm_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     prepared = true;
   }
   const int tiles = (entries + GM - 1) / GM + experts;       // at most this many row tiles, whatever the routing
-  sprout_launch(moe_gemm_mma_kernel<true>, dim3(tiles, (ff + GN / 2 - 1) / (GN / 2)), dim3(GTHREADS), GEMM_SMEM, stream,
-                (const __nv_bfloat16*)h, h_stride, order, offsets, (const __nv_bfloat16*)w_gate_up, act, experts, top, ff, width,
-                limit, alpha);
+  if (limit > 0.f)
+    sprout_launch(moe_gemm_mma_kernel<1>, dim3(tiles, (ff + GN / 2 - 1) / (GN / 2)), dim3(GTHREADS), GEMM_SMEM, stream,
+                  (const __nv_bfloat16*)h, h_stride, order, offsets, (const __nv_bfloat16*)w_gate_up, act, experts, top, ff, width,
+                  limit, alpha);
+  else
+    sprout_launch(moe_gemm_mma_kernel<2>, dim3(tiles, (ff + GN - 1) / GN), dim3(GTHREADS), GEMM_SMEM, stream,
+                  (const __nv_bfloat16*)h, h_stride, order, offsets, (const __nv_bfloat16*)w_gate_up, act, experts, top, ff, width,
+                  limit, alpha);
   if (int code = sprout_check_launch("moe_up_mma")) return code;
-  sprout_launch(moe_gemm_mma_kernel<false>, dim3(tiles, (width + GN - 1) / GN), dim3(GTHREADS), GEMM_SMEM, stream,
+  sprout_launch(moe_gemm_mma_kernel<0>, dim3(tiles, (width + GN - 1) / GN), dim3(GTHREADS), GEMM_SMEM, stream,
                 (const __nv_bfloat16*)act, ff, order, offsets, (const __nv_bfloat16*)w_down, (void*)rows_out, experts, top, width, ff,
                 0.f, 0.f);
   return sprout_check_launch("moe_down_mma");

@@ -67,19 +67,27 @@ _SIGNATURES = {
     "sprout_gated_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _I, _F, _P],
     "sprout_relu2": [_P, _P, _I, _L, _P],
     "sprout_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
-    "sprout_rope_maps_append": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
-    "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _P, _P, _I, _P, _P],
-    "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P, _I, _I, _P, _P, _I, _P, _P],
+    "sprout_rope_maps_append": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P],
+    "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _P, _P, _I, _I, _F, _P, _P],
+    "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P, _I, _I, _P, _P, _I, _I, _F, _P, _P],
     "sprout_multimap_attention_mma_supported": [_I, _I, _I],
     "sprout_decay_chunks": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_decay_chunks_supported": [_I, _I, _I],
     "sprout_decay_scan": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P,
-                          _I, _I, _I, _P, _P, _P, _P, _P],
+                          _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
     "sprout_causal_conv": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gated_group_norm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
     "sprout_scaled_sum": [_P, _P, _F, _P, _F, _L, _P],
-    "sprout_moe_route": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "sprout_moe_route": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _I, _P],
+    "sprout_exp_gates": [_P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P],
+    "sprout_exp_memory_out": [_P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P],
+    "sprout_unit_act": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "sprout_side_gate": [_P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _P, _P],
+    "sprout_rms_add": [_P, _P, _P, _I, _I, _F, _P],
+    "sprout_add_rows": [_P, _P, _P, _I, _I, _P],
+    "sprout_gated_rows_add": [_P, _P, _P, _I, _I, _I, _P],
+    "sprout_narrow_rows": [_P, _P, _L, _P],
     "sprout_moe_arrange": [_P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_moe_up_plain": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
     "sprout_moe_down_plain": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -1154,14 +1162,19 @@ def glu_clamped(gate_up, out, limit: float, alpha: float):
 
 def rope_maps_append(rows, positions, seq_of_token, block_table, cos_table, sin_table, k_cache, v_cache, q_vectors: int,
                      kv_heads: int, maps: int, dim: int, vdim: int, page_tokens: int, write: bool, status,
-                     unit_eps: float = 0.0, value_from_key: bool = False):
+                     unit_eps: float = 0.0, value_from_key: bool = False, q_weight=None, k_weight=None, weight_eps: float = 0.0):
     """Rotate the first ``2 * cos_table.shape[1]`` elements of every query vector (in place) and key vector by the token's
     position, half-split pairs; append keys ([pages, kv_heads, page_tokens, maps * dim]) and values
     ([pages, kv_heads, page_tokens, vdim]) when ``write``.  A row holds q_vectors * dim query elements, then (when
     ``write``) kv_heads * maps * dim key elements and kv_heads * vdim value elements.  With ``unit_eps`` > 0 every query
     and key vector is divided by its root mean square over ``dim`` after the rotation; with ``value_from_key`` the rows hold
-    no value elements and the cached value row is the key row as projected (before rotation and norm)."""
+    no value elements and the cached value row is the key row as projected (before rotation and norm).  ``q_weight`` /
+    ``k_weight`` (float32 [dim]): before the rotation every query / key vector is divided by its root mean square over
+    ``dim`` (``weight_eps`` inside the root) and multiplied by the weight."""
     _rows_contiguous(rows, "rows")
+    for weight in (q_weight, k_weight):
+        if weight is not None and (weight.dtype != torch.float32 or weight.numel() != dim or not weight.is_contiguous()):
+            raise KernelError("rope_maps_append: a norm weight is float32 [dim]")
     _rows_contiguous(block_table, "block_table")
     T = rows.shape[0]
     cos_ptr, sin_ptr, max_positions, rot = _rotary(cos_table, sin_table, dim, "rope_maps_append")
@@ -1175,21 +1188,25 @@ def rope_maps_append(rows, positions, seq_of_token, block_table, cos_table, sin_
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0), cos_ptr, sin_ptr, max_positions,
          _ptr(k_cache, "k_cache", allow_none=not write), _ptr(v_cache, "v_cache", allow_none=not write), T, q_vectors,
          kv_heads, maps, dim, rot, vdim, page_tokens, k_cache.shape[0] if write else 1, 1 if write else 0,
-         float(unit_eps), 1 if value_from_key else 0, _ptr(status, "status", torch.int32), _stream())
+         float(unit_eps), 1 if value_from_key else 0, _ptr(q_weight, "q_weight", torch.float32, True),
+         _ptr(k_weight, "k_weight", torch.float32, True), float(weight_eps), _ptr(status, "status", torch.int32), _stream())
 
 
 MASK_KINDS = {"causal": 0, "window": 1, "chunk": 2}
 
 
-def _mask_code(mask) -> tuple[int, int]:
-    """(kind, size) of ``mask``: None or ("causal", None), ("window", n): a query sees itself and the n - 1 positions
-    before it, ("chunk", n): a query sees the positions of its own chunk of n, counted from position 0, up to itself."""
+def _mask_code(mask) -> tuple[int, int, int]:
+    """(kind, size, kept first positions) of ``mask``: None or ("causal", None), ("window", n) or ("window", n, first): a
+    query sees itself and the n - 1 positions before it, and the first ``first`` positions of its sequence; ("chunk", n):
+    a query sees the positions of its own chunk of n, counted from position 0, up to itself."""
     if mask is None:
-        return 0, 0
-    kind, size = mask
-    if kind not in MASK_KINDS or (kind != "causal" and (not isinstance(size, int) or size <= 0)):
+        return 0, 0, 0
+    kind, size = mask[0], mask[1]
+    keep = int(mask[2]) if len(mask) > 2 else 0
+    if kind not in MASK_KINDS or (kind != "causal" and (not isinstance(size, int) or size <= 0)) or keep < 0 \
+            or (keep and kind != "window"):
         raise KernelError(f"attention: unknown mask {mask!r}")
-    return MASK_KINDS[kind], int(size or 0)
+    return MASK_KINDS[kind], int(size or 0), keep
 
 
 def _gate_args(gate, tokens: int, heads: int, dtype, name: str):
@@ -1201,14 +1218,15 @@ def _gate_args(gate, tokens: int, heads: int, dtype, name: str):
 
 
 def multimap_attention_simple(q, cache, ctx, out, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float,
-                              lam: float, norm_eps: float, out_scale: float, status, mask=None, sink=None, gate=None):
+                              lam: float, norm_eps: float, out_scale: float, status, mask=None, sink=None, gate=None,
+                              softcap: float = 0.0):
     """Causal attention with ``maps`` (1 or 2) softmax maps per head over shared values, float32 arithmetic:
     out = (a_0 - lam a_1) [/ rms when norm_eps > 0] * out_scale per head.  q [tokens, heads * maps * dim] (a view with
     unit inner stride), out [tokens, heads * vdim].  ``mask`` says what a query sees (``_mask_code``), ``sink`` (float32
     [heads]) adds exp(sink_h) to every softmax denominator of head h, ``gate`` ([tokens, heads]) multiplies head h's output
-    by sigmoid(gate)."""
+    by sigmoid(gate); ``softcap`` > 0 turns every scaled score s into softcap * tanh(s / softcap)."""
     _rows_contiguous(q, "q")
-    mask_kind, mask_size = _mask_code(mask)
+    mask_kind, mask_size, mask_keep = _mask_code(mask)
     gate_ptr, gate_stride = _gate_args(gate, q.shape[0], heads, q.dtype, "multimap_attention")
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads):
         raise KernelError("multimap_attention: one float32 sink per head")
@@ -1225,7 +1243,8 @@ def multimap_attention_simple(q, cache, ctx, out, heads: int, kv_heads: int, map
          _ptr(ctx.seq_of_token, "seq_of_token", torch.int32), _ptr(ctx.positions, "positions", torch.int32), _ptr(out, "out"),
          out.stride(0), _dtype_code(q.dtype), q.shape[0], heads, kv_heads, maps, dim, vdim, cache.page_tokens,
          k_cache.shape[0], float(scale), float(lam), float(norm_eps), float(out_scale), mask_kind, mask_size,
-         _ptr(sink, "sink", torch.float32, True), gate_ptr, gate_stride, _ptr(status, "status", torch.int32), _stream())
+         _ptr(sink, "sink", torch.float32, True), gate_ptr, gate_stride, mask_keep, float(softcap),
+         _ptr(status, "status", torch.int32), _stream())
 
 
 # ---------------------------------------------------------------------------------- linear attention with decay and state
@@ -1247,19 +1266,29 @@ def decay_scan(rows, q_start, state_slots, state, decay, out, heads: int, dim: i
 
 # ---------------------------------------------------------------------------------- routed feed-forward
 
-def moe_route(h, router, correction, ids, weights, counts, experts: int, top: int, scale: float):
+def moe_route(h, router, correction, ids, weights, counts, experts: int, top: int, scale: float, groups=None,
+              renormalize: bool = True, extra_out=None):
     """Per token: softmax of the float32 router product, ``top`` largest of score + correction (lowest index first among
-    equals), weights = taken scores / (their sum + 1e-20) * scale.  ids int32 [tokens, top] (from ``experts`` on:
-    identity experts), weights float32 [tokens, top]; counts int32 [experts] += rows per real expert."""
+    equals; ``correction`` None: the scores alone), weights = taken scores / (their sum + 1e-20) * scale, or the taken
+    scores * scale when not ``renormalize``.  ``groups`` = (count, keep): the outputs form ``count`` equal groups of
+    neighbours, a group's score is its largest score, only outputs of the ``keep`` best groups can be taken.  ``extra_out``
+    (float32 [tokens, n]): the router matrix's last n rows are not part of the softmax; their products are written there.
+    ids int32 [tokens, top] (from ``experts`` on: identity experts), weights float32 [tokens, top]; counts int32 [experts] +=
+    rows per real expert."""
     _rows_contiguous(h, "h")
-    outputs, width = router.shape
+    extra = 0 if extra_out is None else extra_out.shape[1]
+    outputs, width = router.shape[0] - extra, router.shape[1]
     T = h.shape[0]
-    if not router.is_contiguous() or h.shape[1] != width or correction.numel() != outputs or tuple(ids.shape) != (T, top) \
+    group_count, group_keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+    if extra and (extra_out.dtype != torch.float32 or not extra_out.is_contiguous() or extra_out.shape[0] != T):
+        raise KernelError("moe_route: extra_out must be contiguous float32 [tokens, extra]")
+    if not router.is_contiguous() or h.shape[1] != width or (correction is not None and correction.numel() != outputs) or tuple(ids.shape) != (T, top) \
             or tuple(weights.shape) != (T, top) or not ids.is_contiguous() or not weights.is_contiguous() or counts.numel() < max(experts, 1):
         raise KernelError("moe_route: shapes do not fit")
     _run("sprout_moe_route", _ptr(h, "h"), h.stride(0), _dtype_code(h.dtype), _ptr(router, "router", torch.float32),
-         _ptr(correction, "correction", torch.float32), _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32),
-         _ptr(counts, "counts", torch.int32), T, width, outputs, experts, top, float(scale), _stream())
+         _ptr(correction, "correction", torch.float32, True), _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32),
+         _ptr(counts, "counts", torch.int32), T, width, outputs, experts, top, float(scale), extra,
+         _ptr(extra_out, "extra_out", torch.float32, True), group_count, group_keep, 1 if renormalize else 0, _stream())
 
 
 def moe_arrange(ids, counts, offsets, order, place_of, experts: int):
@@ -1275,10 +1304,11 @@ def moe_arrange(ids, counts, offsets, order, place_of, experts: int):
 
 def moe_up_plain(h, order, offsets, w_gate_up, act, experts: int, top: int, limit: float, alpha: float):
     """act[row] = glu_clamped(W_gate[e] a, W_up[e] a) for the arranged rows (a = h[order[row] // top], e the row's expert);
-    w_gate_up [experts, 2 ff, width] with gate rows first; CUDA cores, float32 sums in ascending k."""
+    w_gate_up [experts, 2 ff, width] with gate rows first; CUDA cores, float32 sums in ascending k.  ``limit`` <= 0: experts
+    without a gate, act[row] = gelu(W_up[e] a) (the exact form) with w_gate_up [experts, ff, width]."""
     _rows_contiguous(h, "h")
     R, ff = act.shape
-    if not w_gate_up.is_contiguous() or tuple(w_gate_up.shape) != (experts, 2 * ff, h.shape[1]) or w_gate_up.dtype != h.dtype \
+    if not w_gate_up.is_contiguous() or tuple(w_gate_up.shape) != (experts, (2 if limit > 0 else 1) * ff, h.shape[1]) or w_gate_up.dtype != h.dtype \
             or act.dtype != h.dtype or not act.is_contiguous():
         raise KernelError("moe_up: shapes or dtypes do not fit")
     _run("sprout_moe_up_plain", _ptr(h, "h"), h.stride(0), _dtype_code(h.dtype), _ptr(order, "order", torch.int32),
@@ -1321,12 +1351,12 @@ def multimap_key_split(requests: int, kv_heads: int, group: int, max_q_len: int,
 
 def visible_keys(mask, context: int) -> int:
     """The most keys a query of a context of ``context`` positions sees under ``mask``, in whole 64-key tiles' reach."""
-    kind, size = _mask_code(mask)
-    return context if kind == 0 else min(context, size + 63)
+    kind, size, keep = _mask_code(mask)
+    return context if kind == 0 else min(context, size + 63 + (-(-keep // 64) * 64 if keep else 0))
 
 
 def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float, lam: float,
-                       norm_eps: float, out_scale: float, status, mask=None, sink=None, gate=None):
+                       norm_eps: float, out_scale: float, status, mask=None, sink=None, gate=None, softcap: float = 0.0):
     """Attention with one or two maps per head: the tensor-core kernel in bfloat16 for the sizes it is built for
     (``SPROUT_MULTIMAP_ATTENTION=simple`` keeps the float32-arithmetic kernel), else the float32-arithmetic kernel."""
     if q.dtype == torch.bfloat16 and os.environ.get("SPROUT_MULTIMAP_ATTENTION", "mma") != "simple" \
@@ -1347,7 +1377,7 @@ def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int,
         max_q_len = int(getattr(ctx, "max_q_len", 0) or q.shape[0])
         planned = int(getattr(ctx, "planned_context", 0) or getattr(ctx, "max_context", 0) or 0)
         ksplit = multimap_key_split(requests, kv_heads, group, max_q_len, visible_keys(mask, planned)) if planned else 1
-        mask_kind, mask_size = _mask_code(mask)
+        mask_kind, mask_size, mask_keep = _mask_code(mask)
         gate_ptr, gate_stride = _gate_args(gate, q.shape[0], heads, q.dtype, "multimap_attention")
         if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads):
             raise KernelError("multimap_attention: one float32 sink per head")
@@ -1361,11 +1391,11 @@ def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int,
              out.stride(0), requests, tiles, max_q_len, heads, kv_heads, maps, dim, vdim,
              cache.page_tokens, k_cache.shape[0], float(scale),
              float(lam), float(norm_eps), float(out_scale), ksplit, _ptr(partial, "partial", torch.float32, True),
-             mask_kind, mask_size, _ptr(sink, "sink", torch.float32, True), gate_ptr, gate_stride,
+             mask_kind, mask_size, _ptr(sink, "sink", torch.float32, True), gate_ptr, gate_stride, mask_keep, float(softcap),
              _ptr(status, "status", torch.int32), _stream())
         return
     multimap_attention_simple(q, cache, ctx, out, heads, kv_heads, maps, dim, vdim, scale, lam, norm_eps, out_scale, status,
-                              mask=mask, sink=sink, gate=gate)
+                              mask=mask, sink=sink, gate=gate, softcap=softcap)
 
 
 CHUNKED_FROM = 8            # a step whose longest portion has at least this many tokens runs the chunked decay kernel
@@ -1437,27 +1467,42 @@ def _scan_view(t, name: str, width: int, dtype):
 
 
 def gated_scan(q, k, v, z, bias, ctx, state, out, heads: int, groups: int, dim: int, vdim: int, status, per_head: bool = False,
-               tau: float = 1.0, q_scale: float = 1.0, a_log=None, skip=None):
+               tau: float = 1.0, q_scale: float = 1.0, a_log=None, skip=None, given=None, ones_col: bool = False):
     """Per request and head, token by token: S = diag(a) S + (c k) v^T, o = S^T (q_scale q) + skip_h v, the state float32
     [slots, heads, dim, vdim] read and written at the requests' slots (``state``: a ``StateView``-like with ``buffer`` and
     ``slots``).  q, k [tokens, groups * dim] (heads of a group share them), v [tokens, heads * vdim], views with unit inner
     stride of one dtype.  Per key channel (default): z [tokens, heads * dim] (of that dtype or float32), a = sigmoid(z + bias)^(1 / tau), c = 1.
     ``per_head``: z [tokens, heads], dt = softplus(z + bias), a = exp(-exp(a_log) dt) for all of the head's channels, c = dt.
+    ``given`` = (a, c), float32 [tokens, heads] each: the decay and the factor on k per head, ready-made (z and bias are None).
+    ``ones_col``: the state and the output have ``vdim`` columns of which the value rows fill all but the last block of up to
+    four: v is [tokens, heads * v_cols] with v_cols the largest multiple-of-4-aligned count below vdim that the caller
+    chose (``vdim - v.shape[1] // heads`` columns are extra), and column v_cols of the state is fed the constant 1, so that
+    column of the output is (sum of the decayed c k) . q.
     out float32 [tokens, heads * vdim].  A step whose longest portion has ``SCAN_CHUNKED_FROM`` tokens or more cuts the
     portions into chunks of ``SCAN_CHUNK`` tokens that are walked side by side (``SPROUT_GATED_SCAN=whole`` keeps one walk
     per request): scratch for every token's decay and every chunk's sums."""
     tokens, dtype = v.shape[0], v.dtype
+    v_cols = v.shape[1] // heads if ones_col else vdim
+    if ones_col and not v_cols < vdim:
+        raise KernelError("gated_scan: the column of ones needs a state wider than the value rows")
     q_ptr, q_stride = _scan_view(q, "q", groups * dim, dtype)
     k_ptr, k_stride = _scan_view(k, "k", groups * dim, dtype)
-    v_ptr, v_stride = _scan_view(v, "v", heads * vdim, dtype)
-    z_f32 = z.dtype == torch.float32                # the decay's input may be float32 beside bfloat16 projections
-    z_ptr, z_stride = _scan_view(z, "z", heads if per_head else heads * dim, torch.float32 if z_f32 else dtype)
+    v_ptr, v_stride = _scan_view(v, "v", heads * v_cols, dtype)
+    if given is not None:
+        per_head = True
+        z_f32, z_ptr, z_stride = True, None, 0
+        for t in given:
+            if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != tokens * heads:
+                raise KernelError("gated_scan: ready-made decays are contiguous float32 [tokens, heads]")
+    else:
+        z_f32 = z.dtype == torch.float32                # the decay's input may be float32 beside bfloat16 projections
+        z_ptr, z_stride = _scan_view(z, "z", heads if per_head else heads * dim, torch.float32 if z_f32 else dtype)
     buffer = state.buffer
     if buffer.dtype != torch.float32 or not buffer.is_contiguous() or tuple(buffer.shape[1:]) != (heads, dim, vdim):
         raise KernelError("gated_scan: state must be contiguous float32 [slots, heads, dim, vdim]")
     if not out.is_contiguous() or out.dtype != torch.float32 or tuple(out.shape) != (tokens, heads * vdim):
         raise KernelError("gated_scan: out must be contiguous float32 [tokens, heads * vdim]")
-    if bias.numel() != (heads if per_head else heads * dim) or (per_head and (a_log is None or a_log.numel() != heads)) \
+    if given is None and (bias.numel() != (heads if per_head else heads * dim) or (per_head and (a_log is None or a_log.numel() != heads))) \
             or (skip is not None and skip.numel() != heads):
         raise KernelError("gated_scan: the decay's constants do not fit the heads")
     global LAUNCHES
@@ -1466,19 +1511,22 @@ def gated_scan(q, k, v, z, bias, ctx, state, out, heads: int, groups: int, dim: 
     max_chunks = 0
     if getattr(ctx, "max_q_len", 1) >= SCAN_CHUNKED_FROM and os.environ.get("SPROUT_GATED_SCAN", "chunks") != "whole":
         max_chunks = tokens // SCAN_CHUNK + requests
-        da = torch.empty(tokens * (heads if per_head else heads * dim), dtype=torch.float32, device=v.device)
-        dc = torch.empty(tokens * heads, dtype=torch.float32, device=v.device) if per_head else None
+        if given is None:
+            da = torch.empty(tokens * (heads if per_head else heads * dim), dtype=torch.float32, device=v.device)
+            dc = torch.empty(tokens * heads, dtype=torch.float32, device=v.device) if per_head else None
         sums = torch.empty((max_chunks, heads, dim, vdim), dtype=torch.float32, device=v.device)
         prods = torch.empty((max_chunks, heads, dim), dtype=torch.float32, device=v.device)
-        LAUNCHES += 3               # decays, chunk sums and the carry behind the same call
+        LAUNCHES += 3 if given is None else 2               # decays, chunk sums and the carry behind the same call
+    if given is not None:
+        da, dc = given
     _run("sprout_gated_scan", q_ptr, q_stride, k_ptr, k_stride, v_ptr, v_stride, z_ptr, z_stride, 1 if z_f32 else 0,
-         _dtype_code(dtype), _ptr(bias, "bias", torch.float32), _ptr(a_log, "a_log", torch.float32, True), _ptr(skip, "skip", torch.float32, True),
-         1.0 / float(tau), float(q_scale), 1 if per_head else 0, state.slots.numel(), heads, groups, dim, vdim,
+         _dtype_code(dtype), _ptr(bias, "bias", torch.float32, True), _ptr(a_log, "a_log", torch.float32, True), _ptr(skip, "skip", torch.float32, True),
+         1.0 / float(tau), float(q_scale), 2 if given is not None else 1 if per_head else 0, state.slots.numel(), heads, groups, dim, vdim,
          _ptr(ctx.q_start, "q_start", torch.int32), _ptr(state.slots, "state_slots", torch.int32),
          _ptr(buffer, "state", torch.float32), buffer.shape[0], _ptr(out, "out", torch.float32),
          _ptr(status, "status", torch.int32), tokens, SCAN_CHUNK, max_chunks, _ptr(da, "decays", torch.float32, True),
          _ptr(dc, "steps", torch.float32, True), _ptr(sums, "sums", torch.float32, True), _ptr(prods, "products", torch.float32, True),
-         _stream())
+         v_cols, 1 if ones_col else 0, _stream())
 
 
 def causal_conv(rows, weight, bias, out, ctx, state, status, silu: bool = True):
@@ -1523,6 +1571,111 @@ def scaled_sum(x, y1, a: float, y2=None, b: float = 0.0):
         raise KernelError("scaled_sum: contiguous float32 tensors of one shape")
     _run("sprout_scaled_sum", _ptr(x, "x", torch.float32), _ptr(y1, "y1", torch.float32), float(a),
          _ptr(y2, "y2", torch.float32, True), float(b), x.numel(), _stream())
+
+
+# ---------------------------------------------------------------------------------- a matrix memory with exponential gates
+
+def exp_gates(zi, zf, bias_i, bias_f, cap: float, ctx, top_state, slots, status):
+    """The gates of a matrix memory with exponential gates and a running maximum, for every token of the step: with
+    i = cap tanh((zi + bias_i) / cap) and f = logsigmoid(cap tanh((zf + bias_f) / cap)) (``cap`` <= 0: no cap) per head, and m
+    the running maximum carried in ``top_state`` (float32 [slots, heads], zero for a new request):
+    m_t = max(f_t + m_(t-1), i_t), a_t = exp(f_t + m_(t-1) - m_t), c_t = exp(i_t - m_t).  zi, zf: float32 [tokens, heads] views
+    with one row stride.  Returns (a, c, m), float32 [tokens, heads] each; ``top_state`` is brought up to date."""
+    tokens, heads = zi.shape
+    if zi.dtype != torch.float32 or zf.dtype != torch.float32 or zi.stride(1) != 1 or zf.stride(1) != 1 or zf.shape != zi.shape \
+            or zi.stride(0) != zf.stride(0):
+        raise KernelError("exp_gates: the gates' inputs are float32 [tokens, heads] views of equal strides")
+    if top_state.dtype != torch.float32 or not top_state.is_contiguous() or tuple(top_state.shape[1:]) != (heads,):
+        raise KernelError("exp_gates: the running maxima are contiguous float32 [slots, heads]")
+    a, c, m = (torch.empty((tokens, heads), dtype=torch.float32, device=zi.device) for _ in range(3))
+    _run("sprout_exp_gates", zi.data_ptr(), zf.data_ptr(), zi.stride(0), _ptr(bias_i, "bias_i", torch.float32, True),
+         _ptr(bias_f, "bias_f", torch.float32, True), float(cap), slots.numel(), heads, _ptr(ctx.q_start, "q_start", torch.int32),
+         _ptr(slots, "state_slots", torch.int32), _ptr(top_state, "top_state", torch.float32), top_state.shape[0],
+         _ptr(a, "a", torch.float32), _ptr(c, "c", torch.float32), _ptr(m, "m", torch.float32), _ptr(status, "status", torch.int32),
+         _stream())
+    return a, c, m
+
+
+def exp_memory_out(o, m, gate, weight, out, heads: int, vdim: int, eps: float, out_scale: float = 1.0):
+    """The scan's rows into the mixer's gated, normed output: o float32 [tokens, heads * cols] holds per head ``vdim`` outputs
+    and then n . q; out[t, h] = (o / (max(|n . q|, exp(-m)) + 1e-6)) / rms * weight[h] * sigmoid(gate[t, h]) * out_scale, rms over
+    the head's ``vdim`` values (eps inside the root).  gate: a [tokens, heads * vdim] view (float32, or out's dtype)."""
+    tokens = o.shape[0]
+    cols = o.shape[1] // heads
+    _rows_contiguous(gate, "gate")
+    if o.dtype != torch.float32 or not o.is_contiguous() or cols <= vdim or m.numel() != tokens * heads or weight.numel() != heads * vdim \
+            or tuple(out.shape) != (tokens, heads * vdim) or not out.is_contiguous() or gate.shape[1] != heads * vdim \
+            or gate.dtype not in (torch.float32, out.dtype):
+        raise KernelError("exp_memory_out: shapes or dtypes do not fit")
+    _run("sprout_exp_memory_out", _ptr(o, "o", torch.float32), cols, _ptr(m, "m", torch.float32), gate.data_ptr(), gate.stride(0),
+         1 if gate.dtype == torch.float32 else 0, _ptr(weight, "weight", torch.float32), _ptr(out, "out"), _dtype_code(out.dtype),
+         tokens, heads, vdim, float(eps), float(out_scale), _stream())
+
+
+# ---------------------------------------------------------------------------------- rows of feed-forwards and of inputs to the stream
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2}
+
+
+def unit_act(rows, out, activation: str, gated: bool):
+    """out = act(gate) * up for rows [gate: ff | up: ff] (``gated``), or act(rows) for rows of ff elements; ``rows`` and
+    ``out`` are views with unit inner stride of one dtype."""
+    _rows_contiguous(rows, "rows")
+    _rows_contiguous(out, "out")
+    ff = out.shape[1]
+    if activation not in ACTIVATIONS or rows.dtype != out.dtype or rows.shape[0] != out.shape[0] or rows.shape[1] < (2 if gated else 1) * ff:
+        raise KernelError("unit_act: shapes, dtypes or the activation's name do not fit")
+    _run("sprout_unit_act", rows.data_ptr(), rows.stride(0), out.data_ptr(), out.stride(0), _dtype_code(out.dtype), out.shape[0], ff,
+         ACTIVATIONS[activation], 1 if gated else 0, _stream())
+
+
+def side_gate(z, table, first: int, token_ids, out, status):
+    """out[t, j] = gelu_tanh(z[t, j]) * table[token_ids[t], first + j]; z a view with unit inner stride, table contiguous
+    [vocab, columns], out contiguous [tokens, dim], all of one dtype."""
+    _rows_contiguous(z, "z")
+    tokens, dim = out.shape
+    if z.dtype != out.dtype or table.dtype != out.dtype or not table.is_contiguous() or not out.is_contiguous() \
+            or z.shape[0] != tokens or z.shape[1] < dim or first < 0 or first + dim > table.shape[1] or token_ids.numel() != tokens:
+        raise KernelError("side_gate: shapes or dtypes do not fit")
+    _run("sprout_side_gate", z.data_ptr(), z.stride(0), _ptr(table, "table"), table.shape[1], int(first),
+         _ptr(token_ids, "token_ids", torch.int32), table.shape[0], _ptr(out, "out"), _dtype_code(out.dtype), tokens, dim,
+         _ptr(status, "status", torch.int32), _stream())
+
+
+def rms_add(y, weight, x, eps: float):
+    """x += y / sqrt(mean(y^2) + eps) * weight, row by row; float32."""
+    if y.dtype != torch.float32 or x.dtype != torch.float32 or y.shape != x.shape or not y.is_contiguous() or not x.is_contiguous() \
+            or weight.numel() != x.shape[1]:
+        raise KernelError("rms_add: contiguous float32 rows of one shape and a weight per column")
+    _run("sprout_rms_add", _ptr(y, "y", torch.float32), _ptr(weight, "weight", torch.float32), _ptr(x, "x", torch.float32),
+         x.shape[0], x.shape[1], float(eps), _stream())
+
+
+def add_rows(x, vec, other=None):
+    """x[t] += vec (+ other[t]); float32."""
+    if x.dtype != torch.float32 or not x.is_contiguous() or vec.numel() != x.shape[1] or not vec.is_contiguous() \
+            or (other is not None and (other.shape != x.shape or not other.is_contiguous() or other.dtype != torch.float32)):
+        raise KernelError("add_rows: contiguous float32 rows and a vector of their width")
+    _run("sprout_add_rows", _ptr(x, "x", torch.float32), _ptr(other, "other", torch.float32, True), _ptr(vec, "vec", torch.float32),
+         x.shape[0], x.shape[1], _stream())
+
+
+def gated_rows_add(x, y, logits):
+    """x[t] += sigmoid(logits[t]) * y[t]; x, y contiguous float32 [tokens, width], logits a float32 view with one number per row."""
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or x.shape != y.shape or not x.is_contiguous() or not y.is_contiguous() \
+            or logits.dtype != torch.float32 or logits.shape[0] != x.shape[0]:
+        raise KernelError("gated_rows_add: shapes or dtypes do not fit")
+    _run("sprout_gated_rows_add", _ptr(x, "x", torch.float32), _ptr(y, "y", torch.float32), logits.data_ptr(), logits.stride(0),
+         x.shape[0], x.shape[1], _stream())
+
+
+def narrow_rows(x):
+    """The float32 rows ``x`` as a new bfloat16 tensor (round to nearest even)."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("narrow_rows: contiguous float32 rows")
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _run("sprout_narrow_rows", _ptr(x, "x", torch.float32), _ptr(out, "out", torch.bfloat16), x.numel(), _stream())
+    return out
 
 
 def describe_status(word: int) -> str:

@@ -92,8 +92,13 @@ class DecoderModel:
         return specs
 
     def state_specs(self):
-        """One StateSpec (or None) per layer."""
-        return [block.mixer.state_spec() for block in self.blocks]
+        """One StateSpec (or a tuple of them, or None) per state entry: entry i < len(layers) is layer i's own; a layer
+        call that names a further entry (a layer that runs several times, each run with a state of its own) adds it."""
+        specs = [block.mixer.state_spec() for block in self.blocks]
+        further = {call.state: call.layer for call in self.spec.order if call.state is not None and call.state >= len(self.blocks)}
+        for entry in range(len(self.blocks), max(further, default=-1) + 1):
+            specs.append(specs[further[entry]] if entry in further else None)
+        return specs
 
     def decode_plan(self, requests: int, max_keys: int, planned_context: int, page_tokens: int):
         """The parts' plans for a step of one token per request (see ``Part.decode_plan``)."""
@@ -117,7 +122,7 @@ class DecoderModel:
         primed = None
         for n, call in enumerate(self.spec.order):
             cache = storage.view(call.cache, ctx, write=call.writes_cache)
-            state = storage.state_view(call.layer, ctx)
+            state = storage.state_view(call.layer if call.state is None else call.state, ctx)
             block = self.blocks[call.layer]
             if fuses and hasattr(block, "readers"):
                 following = self.blocks[self.spec.order[n + 1].layer] if n + 1 < len(self.spec.order) else None

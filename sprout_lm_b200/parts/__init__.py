@@ -1,7 +1,7 @@
 from .base import (CacheSpec, CacheView, Part, Runtime, StateSpec, StateView, TensorDecl, WeightSource,
                    build_part, register_part, registered_parts)
-from . import (attention, block, decay_attention, embedding, gated_recurrence, latent_attention, mlp,  # noqa: F401
-               multimap_attention, norm, parallel, rope, stream)  # noqa: F401  (register the built-in parts)
+from . import (attention, block, decay_attention, embedding, exp_gated_memory, gated_recurrence, latent_attention, mlp,  # noqa: F401
+               multimap_attention, norm, parallel, rope, side_input, stream)  # noqa: F401  (register the built-in parts)
 from .block import build_block
 from .linear import Linear
 

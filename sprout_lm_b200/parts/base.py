@@ -27,6 +27,8 @@ Categories and what each must provide:
 * ``stream``:        what goes from one layer call to the next when that is more than the layer's
                      result: ``begin(x, calls) -> carry`` after the embedding, ``after(carry, n, x)``
                      after the n-th call of the run order (replaces ``x`` in place).
+* ``side_input``:    something a layer adds to the stream after its sublayers, from the step's token ids:
+                     ``forward(x, ctx)`` adds into ``x`` in place.
 
 ``ctx`` is the step's batch on the device (``engine.batch.StepContext``); ``cache`` a
 ``CacheView`` of the cache slot the call reads (and writes); ``state`` a ``StateView`` or None.
@@ -40,7 +42,7 @@ import torch
 
 from ..config.specs import ConfigError, PartSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream", "side_input")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 
@@ -85,12 +87,14 @@ class CacheSpec:
     """What a mixer keeps per token: keys and values of ``kv_heads`` heads of ``head_dim``.
     kind ``full`` keeps every position, ``window`` the last ``window``.  ``value_dim`` is the width of a
     value row when it differs from a key row's (None: ``head_dim``); 0 means the mixer keeps no values of
-    their own (it reads them out of the key rows), and the slot then has no value buffer."""
+    their own (it reads them out of the key rows), and the slot then has no value buffer.  ``keep_first`` (a window only):
+    the sequence's first positions up to that number stay visible to every later query, so their pages are kept."""
     kv_heads: int
     head_dim: int
     kind: str = "full"
     window: int | None = None
     value_dim: int | None = None
+    keep_first: int = 0
 
     @property
     def value_width(self) -> int:
@@ -98,7 +102,7 @@ class CacheSpec:
 
     @property
     def group_key(self):
-        return (self.kind, self.window)
+        return (self.kind, self.window, self.keep_first)
 
 
 @dataclass(frozen=True)

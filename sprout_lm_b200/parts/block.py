@@ -159,3 +159,38 @@ class SandwichNormBlock(Part):
         y.zero_()
         self.feed_forward.forward(h, y, ctx)
         kernels.norm_add(y, self.norms[3].gain, x, self.norms[3].eps)
+
+
+@register_part("block", "parallel_residual")
+class ParallelResidualBlock(Part):
+    """One norm whose output both sublayers read: h = norm_0(x), x += mixer(h) + ffn(h).  A layer without a feed-forward
+    (``feed_forward.kind == "none"``) adds the mixer alone.  ``options["side"]`` (a ``side_input`` PartSpec) runs after the
+    sublayers and adds to the stream what it makes from the step's token ids.  The stream and the sum are float32."""
+
+    def __init__(self, prefix: str, layer: LayerSpec):
+        self.has_ffn = layer.feed_forward.kind != "none"
+        if len(layer.norms) != 1:
+            raise ValueError("a parallel_residual block has one norm")
+        self.norms = [build_part("norm", layer.norms[0], prefix)]
+        self.mixer = build_part("mixer", layer.mixer, prefix)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, prefix) if self.has_ffn else None
+        side = layer.options.get("side")
+        self.side = build_part("side_input", side, prefix) if side is not None else None
+
+    def parts(self):
+        return [*self.norms, self.mixer, *([self.feed_forward] if self.has_ffn else []), *([self.side] if self.side else [])]
+
+    def tensor_decls(self):
+        return [decl for part in self.parts() for decl in part.tensor_decls()]
+
+    def load(self, source):
+        for part in self.parts():
+            part.load(source)
+
+    def forward(self, x, ctx, cache, state):
+        h = self.norms[0].forward(x)
+        self.mixer.forward(h, x, ctx, cache, state)
+        if self.has_ffn:
+            self.feed_forward.forward(h, x, ctx)
+        if self.side is not None:
+            self.side.forward(x, ctx)

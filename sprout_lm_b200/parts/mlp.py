@@ -179,6 +179,56 @@ class ClampedGLUMLP(Part):
         self.layer.forward(h, x)
 
 
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(Part):
+    """x += W_down (act(W_gate h) * (W_up h)), no biases; ``activation`` is "silu", "gelu_tanh" (the tanh form of gelu) or
+    "gelu_erf" (the exact form).  Gate rows first, then up rows, in one fused product; the activation is a kernel of its
+    own (float32 arithmetic on the product's rounded results)."""
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh", names: dict | None = None):
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("gated_mlp: sizes must be positive")
+        if activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"gated_mlp: unknown activation {activation!r}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        names = names or {"gate": "gate", "up": "up", "down": "down"}
+        self.names = {key: prefix + value for key, value in names.items()}
+        self.gate_up = self.down = None
+
+    def tensor_decls(self):
+        return [TensorDecl(self.names["gate"], (self.intermediate_size, self.hidden_size)),
+                TensorDecl(self.names["up"], (self.intermediate_size, self.hidden_size)),
+                TensorDecl(self.names["down"], (self.hidden_size, self.intermediate_size))]
+
+    def load(self, source: WeightSource):
+        status = source.runtime.status
+        gate, up = source.raw(self.names["gate"]), source.raw(self.names["up"])
+        self.gate_up = Linear(source.to_device_matrix(torch.cat([gate, up], dim=0)), None, status, any_inner_size=True)
+        self.down = Linear(source.matrix(self.names["down"]), None, status, any_inner_size=True)
+
+    def forward(self, h, x, ctx=None):
+        gate_up = self.gate_up.forward(h)
+        act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        kernels.unit_act(gate_up, act, self.activation, gated=True)
+        self.down.forward(act, residual=x)
+
+
+class PlainUnit:
+    """W_down act(W_up h): one expert without a gate."""
+
+    def __init__(self, up, down, activation: str, source: WeightSource):
+        status = source.runtime.status
+        self.activation, self.ff = activation, up.shape[0]
+        self.up = Linear(source.to_device_matrix(up), None, status, any_inner_size=True)
+        self.down = Linear(source.to_device_matrix(down), None, status, any_inner_size=True)
+
+    def forward(self, h, x):
+        """x += the unit's output."""
+        z = self.up.forward(h)
+        kernels.unit_act(z, z, self.activation, gated=False)
+        self.down.forward(z, residual=x)
+
+
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
     """A mixture of small feed-forward layers of which each token uses ``top``.
@@ -189,24 +239,45 @@ class RoutedExperts(Part):
     Experts and the optional shared expert (run for every token and added) are ``ClampedGLU`` layers with sizes and
     limits of their own.  x += weighted sum of the taken experts' outputs (+ shared expert).
 
+    Options: ``expert_kind`` = "plain": experts (and the shared one) are W_down gelu(W_up h) with the exact gelu, no gate
+    and no limit; ``correction`` False: the scores alone decide; ``renormalize`` False: the weights are the taken scores
+    times ``scale``; ``groups`` = (count, keep): the experts form ``count`` equal groups of neighbours, a group's score is
+    its largest score, and only experts of the ``keep`` best groups can be taken; ``shared_gate``: the shared expert's
+    output is multiplied by sigmoid(w_sg . h), one number per token, its row ``shared.sg`` [1, hidden] multiplied in the
+    router's 32-bit product.
+
     Tensors: ``router`` [experts + identity, hidden], ``correction`` [experts + identity], ``e<i>.gate|up|down``,
-    ``shared.gate|up|down``."""
+    ``shared.gate|up|down`` (no ``gate`` matrices for plain experts), ``shared.sg``."""
 
     def __init__(self, prefix: str, hidden_size: int, experts: int, identity: int, top: int, scale: float, expert_ff: int,
-                 expert_limit: float, alpha: float = 1.702, shared_ff: int | None = None, shared_limit: float | None = None,
-                 names: dict | None = None):
+                 expert_limit: float = 0.0, alpha: float = 1.702, shared_ff: int | None = None, shared_limit: float | None = None,
+                 names: dict | None = None, expert_kind: str = "clamped_glu", correction: bool = True, renormalize: bool = True,
+                 groups=None, shared_gate: bool = False):
         if hidden_size <= 0 or experts < 0 or identity < 0 or experts + identity <= 0 or not 0 < top <= experts + identity:
             raise ValueError("routed_experts: bad sizes")
-        if experts and (expert_ff <= 0 or expert_limit <= 0):
+        if expert_kind not in ("clamped_glu", "plain"):
+            raise ValueError("routed_experts: experts are 'clamped_glu' or 'plain'")
+        self.plain = expert_kind == "plain"
+        if experts and (expert_ff <= 0 or (not self.plain and expert_limit <= 0)):
             raise ValueError("routed_experts: experts need a positive size and limit")
-        if shared_ff is not None and (shared_ff <= 0 or shared_limit is None or shared_limit <= 0):
+        if shared_ff is not None and (shared_ff <= 0 or (not self.plain and (shared_limit is None or shared_limit <= 0))):
             raise ValueError("routed_experts: a shared expert needs a positive size and limit")
+        if groups is not None:
+            count, keep = int(groups[0]), int(groups[1])
+            if count <= 0 or not 0 < keep <= count or (experts + identity) % count or top > keep * ((experts + identity) // count):
+                raise ValueError("routed_experts: the groups must be equal and the kept ones must hold at least `top` experts")
+            groups = (count, keep)
+        if shared_gate and shared_ff is None:
+            raise ValueError("routed_experts: a gate without a shared expert")
+        self.has_correction, self.renormalize, self.groups, self.shared_gate = bool(correction), bool(renormalize), groups, bool(shared_gate)
+        if self.plain:
+            expert_limit = 0.0           # what tells the experts' kernels that there is no gate
         self.hidden_size, self.experts, self.identity, self.top = hidden_size, experts, identity, top
         self.scale, self.expert_ff, self.expert_limit, self.alpha = float(scale), expert_ff, float(expert_limit), float(alpha)
         self.shared_ff, self.shared_limit = shared_ff, shared_limit
         self.prefix = prefix
         base = {"router": "router", "correction": "correction", "expert": "e{}.", "shared": "shared.",
-                "gate": "gate", "up": "up", "down": "down"}
+                "gate": "gate", "up": "up", "down": "down", "shared_gate": "shared.sg"}
         self.names = {**base, **(names or {})}
         self.shared = None
         self.runtime = None
@@ -217,31 +288,42 @@ class RoutedExperts(Part):
 
     def tensor_decls(self):
         outputs = self.experts + self.identity
-        decls = [TensorDecl(self.prefix + self.names["router"], (outputs, self.hidden_size), "bias"),
-                 TensorDecl(self.prefix + self.names["correction"], (outputs,), "bias")]
+        decls = [TensorDecl(self.prefix + self.names["router"], (outputs, self.hidden_size), "bias")]
+        if self.has_correction:
+            decls.append(TensorDecl(self.prefix + self.names["correction"], (outputs,), "bias"))
         for index in [*range(self.experts), *([None] if self.shared_ff else [])]:
             ff = self.shared_ff if index is None else self.expert_ff
             gate, up, down = self._expert_names(index)
-            decls += [TensorDecl(gate, (ff, self.hidden_size)), TensorDecl(up, (ff, self.hidden_size)),
-                      TensorDecl(down, (self.hidden_size, ff))]
+            if not self.plain:
+                decls.append(TensorDecl(gate, (ff, self.hidden_size)))
+            decls += [TensorDecl(up, (ff, self.hidden_size)), TensorDecl(down, (self.hidden_size, ff))]
+        if self.shared_gate:
+            decls.append(TensorDecl(self.prefix + self.names["shared_gate"], (1, self.hidden_size), "bias"))
         return decls
 
     def load(self, source: WeightSource):
         self.runtime = source.runtime
         device = source.runtime.device
         self.router = source.vector(self.prefix + self.names["router"])            # float32: the router's product is 32-bit
-        self.correction = source.vector(self.prefix + self.names["correction"])
+        if self.shared_gate:
+            # the shared expert's gate is one more row of the router's matrix: the same 32-bit product gives it
+            gate_row = source.vector(self.prefix + self.names["shared_gate"]).reshape(1, self.hidden_size)
+            self.router = torch.cat([self.router, gate_row], dim=0).contiguous()
+        self.correction = source.vector(self.prefix + self.names["correction"]) if self.has_correction else None
         if self.experts:
             stacks = [[], []]
             for index in range(self.experts):
-                gate, up, down = (source.raw(name) for name in self._expert_names(index))
-                stacks[0].append(torch.cat([gate, up], dim=0))
-                stacks[1].append(down)
-            self.w_gate_up = source.to_device_matrix(torch.stack(stacks[0]))        # [experts, 2 ff, hidden]
+                gate, up, down = self._expert_names(index)
+                stacks[0].append(source.raw(up) if self.plain else torch.cat([source.raw(gate), source.raw(up)], dim=0))
+                stacks[1].append(source.raw(down))
+            self.w_gate_up = source.to_device_matrix(torch.stack(stacks[0]))        # [experts, 2 ff (plain: ff), hidden]
             self.w_down = source.to_device_matrix(torch.stack(stacks[1]))          # [experts, hidden, ff]
         if self.shared_ff:
-            gate, up, down = (source.raw(name) for name in self._expert_names(None))
-            self.shared = ClampedGLU(gate, up, down, self.shared_limit, self.alpha, source)
+            gate, up, down = self._expert_names(None)
+            if self.plain:
+                self.shared = PlainUnit(source.raw(up), source.raw(down), "gelu_erf", source)
+            else:
+                self.shared = ClampedGLU(source.raw(gate), source.raw(up), source.raw(down), self.shared_limit, self.alpha, source)
         self.counts = torch.zeros(max(self.experts, 1), dtype=torch.int32, device=device)   # left zeroed by every step
         self.offsets = torch.zeros(self.experts + 1, dtype=torch.int32, device=device)
 
@@ -250,7 +332,9 @@ class RoutedExperts(Part):
         entries = tokens * self.top
         ids = torch.empty((tokens, self.top), dtype=torch.int32, device=device)
         weights = torch.empty((tokens, self.top), dtype=torch.float32, device=device)
-        kernels.moe_route(h, self.router, self.correction, ids, weights, self.counts, self.experts, self.top, self.scale)
+        gate_logits = torch.empty((tokens, 1), dtype=torch.float32, device=device) if self.shared_gate else None
+        kernels.moe_route(h, self.router, self.correction, ids, weights, self.counts, self.experts, self.top, self.scale,
+                          groups=self.groups, renormalize=self.renormalize, extra_out=gate_logits)
         place_of = torch.empty(entries, dtype=torch.int32, device=device)
         rows = None
         if self.experts:
@@ -262,6 +346,10 @@ class RoutedExperts(Part):
                                 self.expert_limit, self.alpha)
         else:
             place_of.fill_(-1)
-        if self.shared is not None:
+        if self.shared is not None and self.shared_gate:
+            y = torch.zeros((tokens, self.hidden_size), dtype=torch.float32, device=device)
+            self.shared.forward(h, y)
+            kernels.gated_rows_add(x, y, gate_logits)
+        elif self.shared is not None:
             self.shared.forward(h, x)
         kernels.moe_combine(x, h, ids, weights, place_of, rows, self.top)
