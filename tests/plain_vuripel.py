@@ -113,26 +113,45 @@ def soft_cap(s, cap):
 
 
 # ------------------------------------------------------------------------------------------------ mixers
+def exp_gated_memory(q, k, v, gi, gf, state=None, parts=None):
+    """The recurrence alone: q, k [T, H, D] (q already scaled), v [T, H, V], log gates gi, gf [T, H].  ``state`` = (S [H, D, V],
+    n [H, D], m [H]) to start from (zeros when None).  Returns o [T, H, V] and the state after the last token; a list given as
+    ``parts`` receives what o is made of: S^T q [T, H, V], n . q [T, H] and m [T, H]."""
+    T, H, D = q.shape
+    V = v.shape[2]
+    S, n, top = (np.zeros((H, D, V)), np.zeros((H, D)), np.zeros(H)) if state is None else (a.copy() for a in state)
+    out, above, below, tops = np.zeros((T, H, V)), np.zeros((T, H, V)), np.zeros((T, H)), np.zeros((T, H))
+    for head in range(H):
+        for t in range(T):
+            new_top = max(gf[t, head] + top[head], gi[t, head])
+            keep, take = math.exp(gf[t, head] + top[head] - new_top), math.exp(gi[t, head] - new_top)
+            S[head] = keep * S[head] + take * np.outer(k[t, head], v[t, head])
+            n[head] = keep * n[head] + take * k[t, head]
+            top[head] = new_top
+            above[t, head], below[t, head], tops[t, head] = S[head].T @ q[t, head], n[head] @ q[t, head], new_top
+            out[t, head] = above[t, head] / (max(abs(below[t, head]), math.exp(-new_top)) + 1e-6)
+    if parts is not None:
+        parts += [above, below, tops]
+    return out, (S, n, top)
+
+
+def log_gates(zi, zf, cap):
+    """(log input gate, log forget gate) from the gate projections (biases added)."""
+    if cap:
+        zi, zf = cap * np.tanh(zi / cap), cap * np.tanh(zf / cap)
+    return zi, log_sigmoid(zf)
+
+
 def mlstm(h, w, p, m, eps):
     """The matrix memory: per head S (dim x vdim), n (dim) and a running maximum that starts at 0.
     Returns the mixer's output [tokens, width]."""
     T = h.shape[0]
-    H, D, V, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
+    H, D, V = m["heads"], m["dim"], m["vdim"]
     q = lin(h, w[p + "q"]).reshape(T, H, D) * D ** -0.5
     k = lin(h, w[p + "k"]).reshape(T, H, D)
     v = lin(h, w[p + "v"]).reshape(T, H, V)
-    gi = cap * np.tanh(lin(h, w[p + "i"], w[p + "i.b"], exact=True) / cap)                     # log input gate
-    gf = log_sigmoid(cap * np.tanh(lin(h, w[p + "f"], w[p + "f.b"], exact=True) / cap))        # log forget gate
-    out = np.zeros((T, H, V))
-    for head in range(H):
-        S, n, top = np.zeros((D, V)), np.zeros(D), 0.0
-        for t in range(T):
-            new_top = max(gf[t, head] + top, gi[t, head])
-            keep, take = math.exp(gf[t, head] + top - new_top), math.exp(gi[t, head] - new_top)
-            S = keep * S + take * np.outer(k[t, head], v[t, head])
-            n = keep * n + take * k[t, head]
-            top = new_top
-            out[t, head] = (S.T @ q[t, head]) / (max(abs(n @ q[t, head]), math.exp(-top)) + 1e-6)
+    gi, gf = log_gates(lin(h, w[p + "i"], w[p + "i.b"], exact=True), lin(h, w[p + "f"], w[p + "f.b"], exact=True), m.get("gate_cap"))
+    out, _ = exp_gated_memory(q, k, v, gi, gf)
     out = unit_rms(out, eps).reshape(T, H * V) * w[p + "norm"] * sigmoid(lin(h, w[p + "g"]))
     return lin(out, w[p + "o"])
 
