@@ -1212,6 +1212,256 @@ def timed_rarutar(args) -> dict:
     return result
 
 
+VURIPEL_SHAPES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, softcap=30.0, win_dim=64, win_vdim=128, rotated=32, window=1024,
+               keep_first=4, win_softcap=50.0, mem_heads=16, mem_dim=128, mem_vdim=128, gate_cap=15.0, ff=4096, experts=32, top=4,
+               groups=(4, 2), expert_ff=1024, shared_ff=2048, side_dim=64, vocab=32768),
+    "0.3b": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, softcap=30.0, win_dim=64, win_vdim=128, rotated=32, window=512,
+                 keep_first=4, win_softcap=50.0, mem_heads=8, mem_dim=128, mem_vdim=128, gate_cap=15.0, ff=2048, experts=16, top=4,
+                 groups=(4, 2), expert_ff=512, shared_ff=1024, side_dim=32, vocab=32768),
+}
+
+
+def vuripel_folders(shape: str, layers: int):
+    """(Vuripel folder, Rarutar folder of equal size), random weights, written once.  Vuripel's layers in fours: a matrix
+    memory with a dense feed-forward, attention over everything (sink, gate, capped scores) with routed experts, attention over
+    a window that keeps the first positions with a dense feed-forward, the same with routed experts; the experts' active
+    weights equal the dense feed-forward's (top x 2 matrices of expert_ff + 2 of shared_ff = 3 of ff); a per-layer token input
+    everywhere; all layers form one pass of a loop, so the pass's vector is added.  Rarutar beside it is ``--only rarutar``'s
+    model at the same shape (width, feed-forward, vocabulary, attention heads and window alike)."""
+    from sprout_lm_b200 import parse_config, write_random_model
+    z = VURIPEL_SHAPES[shape]
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    memory = {"heads": z["mem_heads"], "dim": z["mem_dim"], "vdim": z["mem_vdim"], "gate_cap": z["gate_cap"]}
+    full = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "softcap": z["softcap"]}
+    windowed = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["win_dim"], "vdim": z["win_vdim"], "scale": z["win_dim"] ** -0.5,
+                "softcap": z["win_softcap"], "mask": {"size": z["window"], "keep_first": z["keep_first"]},
+                "rot": {"base": 1000000.0, "dims": z["rotated"]}}
+    kinds = [("mlstm", memory, dense), ("attention", full, moe), ("attention_2", windowed, dense), ("attention_2", windowed, moe)]
+    raw = {"architecture": "Vuripel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "token_side": {"dim": z["side_dim"]},
+           "loop": {"start": 0, "stop": layers, "times": 1}, "max_positions": 16384,
+           "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": kinds[i % 4][2]} for i in range(layers)]}
+    folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_vuripel_{shape}_L{layers}"
+    if not (folder / "complete").exists():
+        print(f"[bench] writing random weights to {folder}", file=sys.stderr, flush=True)
+        write_random_model(folder, parse_config(raw), seed=0)
+        (folder / "complete").write_text("ok")
+    return folder, rarutar_folders(shape if shape in RARUTAR_SHAPES else "1b", layers)[0]
+
+
+def timed_vuripel_kernels(shape: str, tokens: int, batch: int, context: int, peak: dict) -> dict:
+    """Vuripel's kernels alone beside the like kernels of the closest models at equal sizes.  Attention over everything with
+    capped scores, a sink and a gate beside Rarutar's attention with a sink and a gate (chunks as long as the prompt), and
+    attention over a window that keeps the first positions beside Rarutar's windowed attention: one prompt of ``tokens`` tokens
+    (executed FLOPs of the visible keys against the measured bf16 rate) and ``batch`` single tokens with ``context`` keys held
+    (bytes of the visible keys against the measured copy rate).  The matrix memory's scan (decays ready-made, a column of ones)
+    beside the scan with a decay per head at the same sizes (bytes against the copy rate, 32-bit operations against the CUDA
+    cores' nominal rate), its gates and its output kernel beside the gated group norm.  The experts without gates beside the
+    gated experts of Letanex at the same sizes, the router with groups beside the one without, the gated gelu beside the clamped
+    gated activation, and the per-layer token input (one launch for few tokens; five for a prompt)."""
+    import torch
+    from types import SimpleNamespace
+    from sprout_lm_b200 import kernels
+    z = VURIPEL_SHAPES[shape]
+    page = 16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = {}
+
+    def rand(*shape_, scale=1.0, dtype=torch.bfloat16):
+        return (torch.randn(*shape_, device="cuda", generator=g) * scale).to(dtype)
+
+    def ctx_for(requests, new, held):
+        return SimpleNamespace(seq_of_token=torch.arange(requests, dtype=torch.int32, device="cuda").repeat_interleave(new),
+                               positions=(torch.arange(new, dtype=torch.int32, device="cuda") + (held - new)).repeat(requests),
+                               q_start=(torch.arange(requests + 1, dtype=torch.int32, device="cuda") * new),
+                               context_lens=torch.full((requests,), held, dtype=torch.int32, device="cuda"), max_q_len=new,
+                               max_context=held, planned_context=0, num_seqs=requests, num_tokens=requests * new,
+                               token_ids=torch.randint(0, z["vocab"], (requests * new,), dtype=torch.int32, device="cuda", generator=g))
+
+    def visible(mask, position):
+        if mask is None:
+            return position + 1
+        kind, size = mask[0], mask[1]
+        keep = mask[2] if len(mask) > 2 else 0
+        if kind == "chunk":
+            return position % size + 1
+        seen = min(position + 1, size)
+        return seen + min(keep, max(0, position + 1 - size))
+
+    heads, kv = z["heads"], z["kv_heads"]
+    variants = (("capped_sink_gate", z["dim"], z["vdim"], None, True, z["softcap"]),
+                ("rarutar_sink_gate", z["dim"], z["vdim"], ("chunk", max(tokens, context)), True, 0.0),
+                ("capped_window_kept", z["win_dim"], z["win_vdim"], ("window", z["window"], z["keep_first"]), False, z["win_softcap"]),
+                ("rarutar_window", z["win_dim"], z["win_vdim"], ("window", z["window"]), False, 0.0))
+    for label, requests, new, held in (("prefill", 1, tokens, tokens), ("decode", batch, 1, context)):
+        pages = -(-held // page)
+        table = torch.full((requests, -(-pages // 64) * 64), -1, dtype=torch.int32, device="cuda")
+        table[:, :pages] = torch.randperm(requests * pages, device="cuda", generator=g).to(torch.int32).reshape(requests, pages)
+        ctx = ctx_for(requests, new, held)
+        for name, dim, vdim, mask, extras, cap in variants:
+            k2, v2 = rand(requests * pages + 1, kv, page, dim), rand(requests * pages + 1, kv, page, vdim)
+            rows = rand(requests * new, heads * dim + 8 * (-(-heads // 8)), scale=0.3)
+            q2, gate = rows[:, :heads * dim], rows[:, heads * dim:heads * dim + heads]
+            o2 = torch.empty(requests * new, heads * vdim, dtype=torch.bfloat16, device="cuda")
+            view = SimpleNamespace(k=k2, v=v2, block_table=table, page_tokens=page, write=False)
+            sink = torch.zeros(heads, device="cuda") if extras else None
+            us = _median_us(lambda: kernels.multimap_attention(q2, view, ctx, o2, heads, kv, 1, dim, vdim, dim ** -0.5, 0.0, 0.0, 1.0, status,
+                                                               mask=mask, sink=sink, gate=gate if extras or mask else None, softcap=cap),
+                            repeats=3 if label == "prefill" else 10)
+            if label == "prefill":
+                seen = sum(visible(mask, p) for p in range(tokens))
+                flops = 2.0 * heads * (dim + vdim) * seen
+                out[f"{name}_prefill"] = {"us": round(us, 1), "visible_pairs": seen, "tflops": round(flops / us / 1e6, 1),
+                                          "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3)}
+            else:
+                seen = visible(mask, context - 1)
+                mb = batch * seen * kv * (dim + vdim) * 2 / 1e6
+                out[f"{name}_decode"] = {"us": round(us, 1), "visible_keys": seen, "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                         "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    try:
+        top_mhz = float(subprocess.run(["nvidia-smi", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits", "-i", "0"],
+                                       capture_output=True, text=True, timeout=20).stdout.split()[0])
+    except (OSError, ValueError, IndexError, subprocess.SubprocessError):
+        top_mhz = 1965.0
+    fp32_tflops = torch.cuda.get_device_properties(0).multi_processor_count * 128 * 2 * top_mhz / 1e6
+    out["fp32_cuda_core_tflops_nominal"] = round(fp32_tflops, 1)
+    mh, md, mv = z["mem_heads"], z["mem_dim"], z["mem_vdim"]
+    cols = (mv + 1 + 3) // 4 * 4
+    width = z["width"]
+    for label, requests, new in (("prefill", 1, tokens), ("decode", batch, 1)):
+        ctx = ctx_for(requests, new, new)
+        n = requests * new
+        slots = torch.arange(requests, dtype=torch.int32, device="cuda")
+        rows = rand(n, mh * (2 * md + 2 * mv) + 2 * mh, scale=0.5, dtype=torch.float32)
+        at = mh * (2 * md + 2 * mv)
+        tops = torch.zeros(requests, mh, device="cuda")
+        bias = torch.zeros(mh, device="cuda")
+        us = _median_us(lambda: kernels.exp_gates(rows[:, at:at + mh], rows[:, at + mh:at + 2 * mh], bias, bias, z["gate_cap"], ctx, tops, slots, status))
+        out[f"exp_gates_{label}"] = {"us": round(us, 1), "mb": round(n * mh * 5 * 4 / 1e6, 3)}
+        a, c, m = kernels.exp_gates(rows[:, at:at + mh], rows[:, at + mh:at + 2 * mh], bias, bias, z["gate_cap"], ctx, tops, slots, status)
+        state = SimpleNamespace(buffer=torch.zeros(requests, mh, md, cols, device="cuda"), slots=slots)
+        o = torch.empty(n, mh * cols, device="cuda")
+        us = _median_us(lambda: kernels.gated_scan(rows[:, :mh * md], rows[:, mh * md:2 * mh * md], rows[:, 2 * mh * md:2 * mh * md + mh * mv], None,
+                                                   None, ctx, state, o, mh, mh, md, cols, status, q_scale=md ** -0.5, given=(a, c), ones_col=True),
+                        repeats=3 if new > 1 else 10)
+        mb = (n * mh * ((2 * md + mv) * 4 + 2 * 4 + cols * 4) + 2 * requests * mh * md * cols * 4) / 1e6
+        out[f"memory_scan_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                       "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
+                                       "of_nominal_fp32_cores": round(6.0 * n * mh * md * cols / us / 1e6 / fp32_tflops, 3)}
+        # the scan with a decay per head that the kernel makes itself, at the same sizes (bfloat16 projections)
+        proj = rand(n, mh * (2 * md + mv) + 8 * (-(-mh // 8)), scale=0.5)
+        state_h = SimpleNamespace(buffer=torch.zeros(requests, mh, md, mv, device="cuda"), slots=slots)
+        y = torch.empty(n, mh * mv, device="cuda")
+        zero, a_log = torch.zeros(mh, device="cuda"), torch.full((mh,), -2.0, device="cuda")
+        us = _median_us(lambda: kernels.gated_scan(proj[:, :mh * md], proj[:, mh * md:2 * mh * md], proj[:, 2 * mh * md:2 * mh * md + mh * mv],
+                                                   proj[:, mh * (2 * md + mv):mh * (2 * md + mv) + mh], zero, ctx, state_h, y, mh, mh, md, mv, status,
+                                                   per_head=True, a_log=a_log), repeats=3 if new > 1 else 10)
+        mb = (n * mh * ((2 * md + mv) * 2 + 2 + mv * 4) + 2 * requests * mh * md * mv * 4) / 1e6
+        out[f"head_decay_scan_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                           "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
+                                           "of_nominal_fp32_cores": round(6.0 * n * mh * md * mv / us / 1e6 / fp32_tflops, 3)}
+        gated = torch.empty(n, mh * mv, dtype=torch.bfloat16, device="cuda")
+        gain = torch.ones(mh * mv, device="cuda")
+        us = _median_us(lambda: kernels.exp_memory_out(o, m, rows[:, mh * (2 * md + mv):at], gain, gated, mh, mv, 1e-5))
+        mb = n * mh * (cols * 4 + mv * 4 + mv * 2) / 1e6
+        out[f"memory_out_{label}"] = {"us": round(us, 1), "mb": round(mb, 2), "gbs": round(mb / us * 1e3),
+                                      "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+        us = _median_us(lambda: kernels.gated_group_norm(y, proj[:, :mh * mv], gain, gated, 1e-5, groups=mh, gate_first=False, silu=True))
+        mb = n * mh * mv * (4 + 2 + 2) / 1e6
+        out[f"gated_group_norm_{label}"] = {"us": round(us, 1), "mb": round(mb, 2), "gbs": round(mb / us * 1e3),
+                                            "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+        # routed experts: without gates (one matrix up) beside with gates (two), at the same sizes and routing
+        experts, top, ff = z["experts"], z["top"], z["expert_ff"]
+        h = rand(n, width, scale=0.5)
+        router = rand(experts, width, scale=0.05, dtype=torch.float32)
+        ids = torch.empty((n, top), dtype=torch.int32, device="cuda")
+        weights = torch.empty((n, top), dtype=torch.float32, device="cuda")
+        counts = torch.zeros(experts, dtype=torch.int32, device="cuda")
+        offsets = torch.zeros(experts + 1, dtype=torch.int32, device="cuda")
+        order = torch.empty(n * top, dtype=torch.int32, device="cuda")
+        place_of = torch.empty(n * top, dtype=torch.int32, device="cuda")
+        for name, groups in (("grouped", z["groups"]), ("free", None)):
+            def route():
+                kernels.moe_route(h, router, None, ids, weights, counts, experts, top, 1.0, groups=groups, renormalize=False)
+                kernels.moe_arrange(ids, counts, offsets, order, place_of, experts)
+            out[f"route_{name}_{label}"] = {"us": round(_median_us(route), 1)}
+        act = torch.empty((n * top, ff), dtype=torch.bfloat16, device="cuda")
+        rows_out = torch.empty((n * top, width), dtype=torch.float32, device="cuda")
+        w_down = rand(experts, width, ff, scale=0.02)
+        for name, mats, limit in (("plain", 1, 0.0), ("gated", 2, 7.0)):
+            w_up = rand(experts, mats * ff, width, scale=0.02)
+            us = _median_us(lambda: kernels.moe_experts(h, order, offsets, w_up, w_down, act, rows_out, experts, top, limit, 1.702),
+                            repeats=3 if new > 1 else 10)
+            flops = 2.0 * n * top * width * ff * (mats + 1)
+            touched = min(experts, n * top)
+            mb = touched * (mats + 1) * ff * width * 2 / 1e6
+            out[f"experts_{name}_{label}"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1),
+                                              "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3), "weights_mb": round(mb, 1),
+                                              "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+            del w_up
+        # activations of the dense feed-forward
+        gate_up = rand(n, 2 * z["ff"], scale=1.0)
+        dense_act = torch.empty((n, z["ff"]), dtype=torch.bfloat16, device="cuda")
+        mb = n * z["ff"] * 3 * 2 / 1e6
+        for name, call in (("gated_gelu", lambda: kernels.unit_act(gate_up, dense_act, "gelu_tanh", gated=True)),
+                           ("clamped_glu", lambda: kernels.glu_clamped(gate_up, dense_act, 7.0, 1.702))):
+            us = _median_us(call)
+            out[f"{name}_{label}"] = {"us": round(us, 1), "mb": round(mb, 2), "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+        # the per-layer token input
+        from sprout_lm_b200.config.specs import PartSpec
+        from sprout_lm_b200.parts import Runtime, WeightSource, build_part
+        side = build_part("side_input", PartSpec("gated_token_row", {"hidden_size": width, "vocab_size": z["vocab"], "dim": z["side_dim"],
+                                                                     "first": z["side_dim"], "columns": 4 * z["side_dim"], "eps": 1e-5,
+                                                                     "declares_table": True}), "l1.")
+        tensors = {"side.embed": rand(z["vocab"], 4 * z["side_dim"]).cpu(), "l1.side.gate": rand(z["side_dim"], width, scale=0.02).cpu(),
+                   "l1.side.proj": rand(width, z["side_dim"], scale=0.02).cpu(), "l1.side.norm": torch.ones(width)}
+        side.load(WeightSource(lambda key: tensors[key], Runtime("cuda:0", torch.bfloat16)))
+        stream = rand(min(n, 32) if new == 1 else n, width, dtype=torch.float32)
+        side_ctx = SimpleNamespace(token_ids=ctx.token_ids[:stream.shape[0]])
+        us = _median_us(lambda: side.forward(stream, side_ctx))
+        mb = (stream.shape[0] * width * 8 + 2 * z["side_dim"] * width * 2) / 1e6
+        out[f"token_input_{label}"] = {"us": round(us, 1), "tokens": stream.shape[0], "mb": round(mb, 2),
+                                       "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    assert int(status.item()) == 0
+    return out
+
+
+def timed_vuripel(args) -> dict:
+    """``--only vuripel``: prefill and decode throughput of Vuripel at ``--shape 1b|0.3b`` (random weights, ``--layers`` layers,
+    4 if not given) beside Rarutar at equal size, through the same runner, and the kernels of both alone."""
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.step import ModelRunner
+    shape = args.shape if args.shape in VURIPEL_SHAPES else "1b"
+    layers = args.layers or 4
+    peak = peaks()
+    vuripel_dir, rarutar_dir = vuripel_folders(shape, layers)
+    prompt_len = args.prompt_len
+    result = {"impl": "ours", "only": "vuripel", "shape": shape, "layers": layers, "dtype": "bf16", "data": "synthetic",
+              "prefill_tokens": args.tokens, "decode_batch": args.batch, "decode_prompt_len": prompt_len, "steps": args.steps,
+              "peaks": {"bf16_tflops": peak["bf16_tflops"], "hbm_gbs": peak["hbm_gbs"], "source": peak.get("source", "measured")}}
+    for tag, folder in (("vuripel", vuripel_dir), ("rarutar", rarutar_dir)):
+        model = load_model(folder, dtype="bfloat16", device="cuda:0")
+        slots = max(64, args.batch)
+        pages = slots * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + args.tokens // 16 + 16
+        runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=slots, prefix_caching=False)
+        rng = np.random.default_rng(0)
+        ms = timed_prefill(runner, args.tokens, rng)
+        decode = timed_decode(runner, args.batch, prompt_len, args.steps, args.warmup, rng)
+        result[tag] = {"weights_mb": round((folder / "model.safetensors").stat().st_size / 1e6, 1), "prefill_ms": round(ms, 3),
+                       "prefill_tokens_per_s": round(args.tokens / ms * 1000),
+                       "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tokens_per_s"]),
+                       "decode_launches_per_step": decode["launches_per_step"]}
+        del runner, model
+        torch.cuda.empty_cache()
+    result["kernels"] = timed_vuripel_kernels(shape, args.tokens, max(args.batch, 64), 2048, peak)
+    return result
+
+
 def run(args) -> dict:
     import numpy as np
     import torch
@@ -1225,6 +1475,8 @@ def run(args) -> dict:
         return timed_letanex(args)
     if args.only == "rarutar":
         return timed_rarutar(args)
+    if args.only == "vuripel":
+        return timed_vuripel(args)
     if args.only == "attention":
         return timed_attention(args.tokens, args.shape)
     if args.only == "gemm":
@@ -1332,7 +1584,7 @@ def main() -> int:
     parser.add_argument("--portion", type=int, default=4096, help="with --only long-prompt: tokens of a step (--tokens: of the whole prompt)")
     parser.add_argument("--prompt-len", type=int, default=512, help="with --only decode: tokens of every request's prompt (the context grows to hold it)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt", "latent", "letanex", "rarutar"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt", "latent", "letanex", "rarutar", "vuripel"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
     parser.add_argument("--shape", choices=sorted(set(SHAPES) | set(LATENT_SHAPES) | set(LETANEX_SHAPES) | set(RARUTAR_SHAPES)), default="0.5b", help="with --only: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")

@@ -56,10 +56,21 @@ exp_gates_kernel(const float* __restrict__ zi, const float* __restrict__ zf, int
     }
     __syncthreads();
     if (tid == 0) {
+      // the chain itself is an add and a max per token; its operands come eight tokens at a time, ahead of it
       float top = tops[0];
-      for (int j = 0; j < n; j++) {
-        top = fmaxf(gf[j] + top, gi[j]);
-        tops[j + 1] = top;
+      for (int j0 = 0; j0 < n; j0 += 8) {
+        float f[8], i[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          f[u] = j0 + u < n ? gf[j0 + u] : 0.f;
+          i[u] = j0 + u < n ? gi[j0 + u] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          if (j0 + u >= n) break;
+          top = fmaxf(f[u] + top, i[u]);
+          tops[j0 + u + 1] = top;
+        }
       }
     }
     __syncthreads();

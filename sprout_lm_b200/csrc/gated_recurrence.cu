@@ -104,7 +104,7 @@ gated_scan_kernel(const ScanParams<T> p, int slices_log2, int batch) {
   pdl_wait();
   const int h = blockIdx.y, tid = threadIdx.x;
   int r = blockIdx.x, chunk_at = 0, chunk_count = 1;
-  if (PHASE != SCAN_WHOLE) {
+  if (PHASE != SCAN_WHOLE && p.sums != nullptr) {      // without scratch every request is one chunk: block x walks request x
     if (!find_chunk(p.q_start, p.requests, p.chunk, blockIdx.x, r, chunk_at, chunk_count)) return;
     if (PHASE == SCAN_CHUNK_SUMS && chunk_at == chunk_count - 1) return;      // nothing comes after it
   }

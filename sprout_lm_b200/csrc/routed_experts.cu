@@ -45,7 +45,7 @@ moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict_
   int outputs = softmax_outputs + extra;              // rows of the router matrix
   float* zs = smem;                                   // ROUTE_TOKENS x outputs: scores
   float* choices = zs + ROUTE_TOKENS * outputs;       // ROUTE_TOKENS x outputs
-  float* rows = choices + ROUTE_TOKENS * outputs;     // ROUTE_TOKENS x width: the tokens' h as float32
+  float* rows = smem + ((2 * ROUTE_TOKENS * outputs + 3) & ~3);   // ROUTE_TOKENS x width: the tokens' h as float32, on a 16-byte boundary
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t0 = blockIdx.x * ROUTE_TOKENS;
@@ -60,10 +60,25 @@ moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict_
     float dot[ROUTE_TOKENS];
 #pragma unroll
     for (int r = 0; r < ROUTE_TOKENS; r++) dot[r] = 0.f;
-    for (int k = lane; k < width; k += 32) {
-      const float wk = w[k];
+    if ((width & 3) == 0) {
+      // four weights a load; a lane's elements are added in ascending k, as in the scalar loop over its own elements
+      for (int k = lane * 4; k < width; k += 128) {
+        const float4 wk = *reinterpret_cast<const float4*>(w + k);
 #pragma unroll
-      for (int r = 0; r < ROUTE_TOKENS; r++) dot[r] = fmaf(rows[r * width + k], wk, dot[r]);
+        for (int r = 0; r < ROUTE_TOKENS; r++) {
+          const float4 xv = *reinterpret_cast<const float4*>(rows + r * width + k);
+          dot[r] = fmaf(xv.x, wk.x, dot[r]);
+          dot[r] = fmaf(xv.y, wk.y, dot[r]);
+          dot[r] = fmaf(xv.z, wk.z, dot[r]);
+          dot[r] = fmaf(xv.w, wk.w, dot[r]);
+        }
+      }
+    } else {
+      for (int k = lane; k < width; k += 32) {
+        const float wk = w[k];
+#pragma unroll
+        for (int r = 0; r < ROUTE_TOKENS; r++) dot[r] = fmaf(rows[r * width + k], wk, dot[r]);
+      }
     }
 #pragma unroll
     for (int r = 0; r < ROUTE_TOKENS; r++) {
@@ -559,8 +574,8 @@ SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const fl
   SPROUT_REQUIRE(tokens > 0 && width > 0 && outputs > 0 && experts >= 0 && experts <= outputs && top > 0 && top <= outputs,
                  "moe_route: bad sizes (outputs %d, experts %d, top %d)", outputs, experts, top);
   const int rows_of_router = outputs + extra;
-  const int per_block = tokens > 64 && (size_t)8 * (2 * rows_of_router + width) * sizeof(float) <= 200 * 1024 ? 8 : 1;
-  const size_t smem = (size_t)per_block * (2 * rows_of_router + width) * sizeof(float);
+  const int per_block = tokens > 64 && ((size_t)8 * (2 * rows_of_router + width) + 4) * sizeof(float) <= 200 * 1024 ? 8 : 1;
+  const size_t smem = ((size_t)per_block * (2 * rows_of_router + width) + 4) * sizeof(float);
   SPROUT_REQUIRE(smem <= 200 * 1024, "moe_route: too many router outputs (%d) or too wide rows (%d)", outputs, width);
   static bool prepared = false;
   if (!prepared) {

@@ -82,7 +82,8 @@ _SIGNATURES = {
     "sprout_moe_route": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _I, _P],
     "sprout_exp_gates": [_P, _P, _I, _P, _P, _F, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P],
     "sprout_exp_memory_out": [_P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P],
-    "sprout_unit_act": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "sprout_unit_act": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+    "sprout_side_input_few": [_P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "sprout_side_gate": [_P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _P, _P],
     "sprout_rms_add": [_P, _P, _P, _I, _I, _F, _P],
     "sprout_add_rows": [_P, _P, _P, _I, _I, _P],
@@ -1617,16 +1618,43 @@ def exp_memory_out(o, m, gate, weight, out, heads: int, vdim: int, eps: float, o
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2}
 
 
-def unit_act(rows, out, activation: str, gated: bool):
+def unit_act(rows, out, activation: str, gated: bool, row_logits=None):
     """out = act(gate) * up for rows [gate: ff | up: ff] (``gated``), or act(rows) for rows of ff elements; ``rows`` and
-    ``out`` are views with unit inner stride of one dtype."""
+    ``out`` are views with unit inner stride of one dtype.  ``row_logits`` (a float32 view with one number per row): row r is
+    also multiplied by sigmoid(row_logits[r])."""
     _rows_contiguous(rows, "rows")
     _rows_contiguous(out, "out")
     ff = out.shape[1]
     if activation not in ACTIVATIONS or rows.dtype != out.dtype or rows.shape[0] != out.shape[0] or rows.shape[1] < (2 if gated else 1) * ff:
         raise KernelError("unit_act: shapes, dtypes or the activation's name do not fit")
+    if row_logits is not None and (row_logits.dtype != torch.float32 or row_logits.shape[0] != out.shape[0]):
+        raise KernelError("unit_act: one float32 logit per row")
     _run("sprout_unit_act", rows.data_ptr(), rows.stride(0), out.data_ptr(), out.stride(0), _dtype_code(out.dtype), out.shape[0], ff,
-         ACTIVATIONS[activation], 1 if gated else 0, _stream())
+         ACTIVATIONS[activation], 1 if gated else 0, None if row_logits is None else row_logits.data_ptr(),
+         0 if row_logits is None else row_logits.stride(0), _stream())
+
+
+SIDE_FEW_TOKENS = 32        # up to this many tokens the per-layer token input runs as two light launches
+SIDE_FEW_MAX_DIM = 512
+
+
+def side_input_few(x, w_gate, w_proj, weight, table, first: int, token_ids, eps: float, status):
+    """x[t] += rmsnorm(W_proj (gelu_tanh(W_gate x[t]) * table[token_ids[t], first : first + dim])) * weight for a handful
+    of tokens in two launches (the gated row; the projection with norm and sum): x float32 [tokens, width], w_gate [dim, width], w_proj [width, dim] and table [vocab, columns]
+    contiguous of one dtype (the stream and the intermediate results are rounded to it as the separate kernels round them)."""
+    tokens, width = x.shape
+    dim = w_gate.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or tuple(w_gate.shape) != (dim, width) or tuple(w_proj.shape) != (width, dim) \
+            or not w_gate.is_contiguous() or not w_proj.is_contiguous() or not table.is_contiguous() or w_gate.dtype != w_proj.dtype \
+            or table.dtype != w_gate.dtype or weight.numel() != width or token_ids.numel() != tokens:
+        raise KernelError("side_input_few: shapes or dtypes do not fit")
+    global LAUNCHES
+    g = torch.empty((tokens, dim), dtype=torch.float32, device=x.device)
+    _run("sprout_side_input_few", _ptr(x, "x", torch.float32), _ptr(w_gate, "w_gate"), _ptr(w_proj, "w_proj"),
+         _ptr(weight, "weight", torch.float32), _ptr(table, "table"), table.shape[1], int(first), _ptr(token_ids, "token_ids", torch.int32),
+         table.shape[0], _dtype_code(w_gate.dtype), tokens, width, dim, float(eps), _ptr(g, "g", torch.float32),
+         _ptr(status, "status", torch.int32), _stream())
+    LAUNCHES += 1               # two kernels behind one call
 
 
 def side_gate(z, table, first: int, token_ids, out, status):

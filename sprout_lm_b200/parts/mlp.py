@@ -222,10 +222,11 @@ class PlainUnit:
         self.up = Linear(source.to_device_matrix(up), None, status, any_inner_size=True)
         self.down = Linear(source.to_device_matrix(down), None, status, any_inner_size=True)
 
-    def forward(self, h, x):
-        """x += the unit's output."""
+    def forward(self, h, x, row_logits=None):
+        """x += the unit's output, row t times sigmoid(row_logits[t]) when given (the factor goes onto the activation's rows:
+        the product after it is linear)."""
         z = self.up.forward(h)
-        kernels.unit_act(z, z, self.activation, gated=False)
+        kernels.unit_act(z, z, self.activation, gated=False, row_logits=row_logits)
         self.down.forward(z, residual=x)
 
 
@@ -346,7 +347,9 @@ class RoutedExperts(Part):
                                 self.expert_limit, self.alpha)
         else:
             place_of.fill_(-1)
-        if self.shared is not None and self.shared_gate:
+        if self.shared is not None and self.shared_gate and self.plain:
+            self.shared.forward(h, x, row_logits=gate_logits)
+        elif self.shared is not None and self.shared_gate:
             y = torch.zeros((tokens, self.hidden_size), dtype=torch.float32, device=device)
             self.shared.forward(h, y)
             kernels.gated_rows_add(x, y, gate_logits)

@@ -44,6 +44,11 @@ class GatedTokenRow(Part):
 
     def forward(self, x, ctx):
         dtype = self.runtime.dtype
+        if x.shape[0] <= kernels.SIDE_FEW_TOKENS and self.dim <= kernels.SIDE_FEW_MAX_DIM and self.hidden_size <= 10240:
+            # a handful of tokens: two light launches (the gated row; the projection with the norm and the sum)
+            kernels.side_input_few(x, self.gate.weight, self.proj.weight, self.gain, self.table, self.first, ctx.token_ids, self.eps,
+                                   self.runtime.status)
+            return
         stream = x if dtype == torch.float32 else kernels.narrow_rows(x)      # the projection reads the stream in the compute dtype
         z = self.gate.forward(stream)
         g = torch.empty((x.shape[0], self.dim), dtype=dtype, device=x.device)

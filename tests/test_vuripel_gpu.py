@@ -71,6 +71,27 @@ def test_row_kernels(dtype):
     assert np.abs(out.float().cpu().numpy() - want).max() <= tol * 4 and int(status.item()) == 0
     kernels.side_gate(dev(z, dtype)[:, :6], dev(table, dtype), 12, ints([1, 2, 23, 3, 4]), out, status)
     assert int(status.item()) == 2                                           # a token beyond the table is flagged, not read
+    status.zero_()
+    # the whole per-layer token input in one launch, for a handful of tokens
+    for width, dim in ((40, 6), (128, 16), (200, 24)):
+        x = rng.normal(0, 2.0, size=(5, width)).astype(np.float32)
+        parts = {"s.gate": rounded(rng.normal(0, 0.3, size=(dim, width)), dtype), "s.proj": rounded(rng.normal(0, 0.3, size=(width, dim)), dtype)}
+        gain = rng.normal(1.0, 0.3, size=width).astype(np.float32)
+        wide = rounded(rng.normal(size=(23, 3 * dim)), dtype)
+        got = dev(x.copy())
+        kernels.side_input_few(got, dev(parts["s.gate"], dtype), dev(parts["s.proj"], dtype), dev(gain), dev(wide, dtype), dim, ints(tokens),
+                               1e-5, status)
+        w = {key: f64(value) for key, value in parts.items()} | {"s.norm": gain.astype(np.float64)}
+        want = plain.token_side(x.astype(np.float64), w, "s.", f64(wide)[tokens][:, dim:2 * dim], 1e-5)
+        assert np.abs(got.cpu().numpy() - want).max() <= (2e-5 if dtype == "float32" else 5e-2), (width, dim)
+    status.zero_()
+    # a gate per row on an activation
+    rows = rounded(rng.normal(0, 2.0, size=(6, 20)), dtype)
+    logits = rng.normal(0, 2.0, size=(6, 2)).astype(np.float32)
+    out = torch.empty(6, 20, dtype=DTYPES[dtype], device=DEV)
+    kernels.unit_act(dev(rows, dtype), out, "gelu_erf", gated=False, row_logits=dev(logits)[:, 1:])
+    want = plain.gelu_erf(f64(rows)) * plain.sigmoid(logits[:, 1:].astype(np.float64))
+    assert (np.abs(out.float().cpu().numpy() - want) <= tol * (1 + np.abs(want))).all()
     if dtype == "bfloat16":
         return
     for width in (40, 257, 1030):
