@@ -1,8 +1,8 @@
 """Command line in the manner of the reference's demo (src/demo.ts) and smoke script
 (scripts/smoke-cuda.ts).
 
-    python -m sprout_lm_b200 demo [--model DIR | --tiny A|B|T|L] [--seed S] [--json] [--pressure] [--dtype bfloat16|float32]
-    python -m sprout_lm_b200 generate (--model DIR | --tiny A|B|T|L) --prompt 1,2,3 [--max-new-tokens N]
+    python -m sprout_lm_b200 demo [--model DIR | --tiny A|B|T|L|V] [--seed S] [--json] [--pressure] [--dtype bfloat16|float32]
+    python -m sprout_lm_b200 generate (--model DIR | --tiny A|B|T|L|V) --prompt 1,2,3 [--max-new-tokens N]
                                       [--temperature T] [--seed S] [--ignore-eos] [--json]
     python -m sprout_lm_b200 random-model --out DIR --config CONFIG.json [--seed S]
 
@@ -71,6 +71,21 @@ TINY_CONFIGS["L"] = {
     "layers": [{"type": "attention", "mixer": _two_maps(4, 2, 16, 32), "mlp": {"kind": "dense", "ff": 256}},
                {"type": "lightning", "mixer": {"heads": 2, "dim": 64, "vdim": 32, "decay": [0.9, 0.99]}, "mlp": _routed(6, 2, 2, 64, 96)},
                {"type": "attention", "mixer": _two_maps(4, 2, 16, 32, kv_from=0), "mlp": _routed(6, 2, 2, 64, 96)}]}
+
+
+# --tiny V: a tiny random Vuripel model (a matrix memory with exponential gates, attention with capped scores, a sink and a
+# gate per head, attention over a window that keeps the first positions; routed experts chosen among the best groups; the
+# first two layers run twice; a per-layer token input)
+TINY_CONFIGS["V"] = {
+    "architecture": "Vuripel", "vocab": 384, "width": 128, "norm": {"eps": 1e-5}, "max_positions": 512, "token_side": {"dim": 16},
+    "loop": {"start": 0, "stop": 2, "times": 2},
+    "layers": [{"type": "mlstm", "mixer": {"heads": 2, "dim": 32, "vdim": 64, "gate_cap": 12.0}, "mlp": {"kind": "dense", "ff": 192}},
+               {"type": "attention_2", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.18, "softcap": 25.0,
+                                                 "mask": {"size": 24, "keep_first": 2}, "rot": {"base": 10000.0, "dims": 16}},
+                "mlp": {"kind": "moe", "expert": {"ff": 48}, "shared": {"ff": 64},
+                        "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}},
+               {"type": "attention", "mixer": {"heads": 4, "kv_heads": 1, "dim": 32, "vdim": 64, "scale": 0.2, "softcap": 15.0},
+                "mlp": {"kind": "dense", "ff": 160}}]}
 
 
 def _table(rows: list[dict]) -> str:
@@ -220,7 +235,8 @@ def main(argv=None) -> int:
         p.add_argument("--model", help="folder with config.json and model.safetensors")
         p.add_argument("--tiny", choices=sorted(TINY) + sorted(TINY_CONFIGS), help="instead of --model: a tiny random model (A: 2 layers, "
                        "hidden 64, 4/2 heads of 16, tied head; B: 3 layers, hidden 96, 3/1 heads of 32, untied head; T: a Tulipel "
-                       "model of 4 latent-attention layers, width 128; L: a Letanex model of 3 layers, width 128), written with --seed")
+                       "model of 4 latent-attention layers, width 128; L: a Letanex model of 3 layers, width 128; V: a Vuripel model of "
+                       "3 layers of which two run twice, width 128), written with --seed")
         p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
         p.add_argument("--seed", type=int, default=0)
     rnd = sub.add_parser("random-model", help="write config.json and model.safetensors with random weights")
