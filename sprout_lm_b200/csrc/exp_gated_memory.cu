@@ -9,9 +9,11 @@
 // a_t and c_t never exceed 1.
 //
 //  * exp_gates:       m_t, a_t, c_t for every token of the step, from and into the requests' state slots (m per head).
-//                     One block per (request, head): the gates of a tile of tokens side by side, the maxima in the
-//                     tokens' order by one thread (an add and a max per token), the exponentials side by side again.
-//                     The result does not depend on how the tokens were cut into steps.
+//                     One block per (request, head): the gates of a tile of tokens side by side, the running maxima by one
+//                     warp, 32 tokens at a time (m -> max(m + f, i) is a pair (f, i), and two steps in a row are the pair
+//                     (f1 + f2, max(i1 + f2, i2)): a prefix scan over pairs with shuffles, then the carry from the tokens
+//                     before), the exponentials side by side again.  Between two ways of cutting the tokens into steps the
+//                     maxima differ by the rounding of the sums of f alone, and a shift of m moves S, n and exp(-m) alike.
 //  * exp_memory_out:  the scan's rows [o | n . q | padding] per head into the mixer's gated, normed output:
 //                     o / (max(|n . q|, exp(-m)) + 1e-6), divided by its root mean square over the head, times a weight,
 //                     times sigmoid(gate), times out_scale.
@@ -55,22 +57,23 @@ exp_gates_kernel(const float* __restrict__ zi, const float* __restrict__ zf, int
       gf[j] = log_sigmoid_f(b);
     }
     __syncthreads();
-    if (tid == 0) {
-      // the chain itself is an add and a max per token; its operands come eight tokens at a time, ahead of it
-      float top = tops[0];
-      for (int j0 = 0; j0 < n; j0 += 8) {
-        float f[8], i[8];
+    if (tid < 32) {
+      float carry = tops[0];
+      for (int j0 = 0; j0 < n; j0 += 32) {
+        const int j = j0 + tid;
+        // beyond the tile's end: the pair that changes nothing, (0, -inf)
+        float a = j < n ? gf[j] : 0.f, b = j < n ? gi[j] : -INFINITY;
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-          f[u] = j0 + u < n ? gf[j0 + u] : 0.f;
-          i[u] = j0 + u < n ? gi[j0 + u] : 0.f;
+        for (int d = 1; d < 32; d <<= 1) {
+          const float ap = __shfl_up_sync(0xffffffffu, a, d), bp = __shfl_up_sync(0xffffffffu, b, d);
+          if (tid >= d) {
+            b = fmaxf(bp + a, b);
+            a = ap + a;
+          }
         }
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-          if (j0 + u >= n) break;
-          top = fmaxf(f[u] + top, i[u]);
-          tops[j0 + u + 1] = top;
-        }
+        const float top = fmaxf(carry + a, b);
+        if (j < n) tops[j + 1] = top;
+        carry = __shfl_sync(0xffffffffu, top, 31);
       }
     }
     __syncthreads();
