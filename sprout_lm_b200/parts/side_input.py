@@ -44,8 +44,10 @@ class GatedTokenRow(Part):
 
     def forward(self, x, ctx):
         dtype = self.runtime.dtype
-        if x.shape[0] <= kernels.SIDE_FEW_TOKENS and self.dim <= kernels.SIDE_FEW_MAX_DIM and self.hidden_size <= 10240:
-            # a handful of tokens: two light launches (the gated row; the projection with the norm and the sum)
+        if dtype != torch.float32 and x.shape[0] <= kernels.SIDE_FEW_TOKENS and self.dim <= kernels.SIDE_FEW_MAX_DIM \
+                and self.hidden_size <= 10240:
+            # a handful of tokens: two light launches (the gated row; the projection with the norm and the sum).  The 32-bit
+            # path keeps the products whose order of additions does not depend on the number of tokens
             kernels.side_input_few(x, self.gate.weight, self.proj.weight, self.gain, self.table, self.first, ctx.token_ids, self.eps,
                                    self.runtime.status)
             return
