@@ -40,9 +40,17 @@ constexpr int STAGING_BYTES = 2 * 128 * 128;    // two [128 rows, 32 float32] ti
 // SwiGLU epilogue: the weight rows interleave gate and up in blocks of 8 (rows 16b..16b+7 gate,
 // 16b+8..16b+15 up), so output feature 8b+j is silu(D[.., 16b+j]) * D[.., 16b+8+j]; the output
 // has N/2 features and is bfloat16.
+// The gate's activation is silu, or (`gelu`) the tanh form of gelu: 0.5 g (1 + tanh(y)) = g sigmoid(2 y) with
+// y = sqrt(2 / pi) (g + 0.044715 g^3).
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float gated_mul(float g, float u, int gelu) {
+  if (!gelu) return silu_mul(g, u);
+  const float y2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+  return __fdividef(g, 1.0f + __expf(-y2)) * u;
+}
 
 struct Params {
+  int gate_gelu;         // the gated epilogue's activation: 0 silu, 1 the tanh form of gelu
   const float* bias;     // [N] or null
   void* out;             // [M, N] row stride ldo, bf16 or f32
   int out_is_f32;
@@ -386,7 +394,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
               const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
               const int m = col0 + c + j;
               if ((lane & 8) == 0 && row < p.N && m < p.M)
-                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_n] = __float2bfloat16_rn(silu_mul(mine, other));
+                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_n] = __float2bfloat16_rn(gated_mul(mine, other, p.gate_gelu));
             }
           } else if (row < p.N) {
             const float b = (p.bias && first_split) ? p.bias[row] : 0.f;
@@ -416,7 +424,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 uint32_t packed[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(v[2 * j], v[2 * j + 8]), silu_mul(v[2 * j + 1], v[2 * j + 9]));
+                  __nv_bfloat162 h = __floats2bfloat162_rn(gated_mul(v[2 * j], v[2 * j + 8], p.gate_gelu), gated_mul(v[2 * j + 1], v[2 * j + 9], p.gate_gelu));
                   packed[j] = *(uint32_t*)&h;
                 }
                 __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * p.ldo + (n_base >> 1);
@@ -539,11 +547,13 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const CUten
 // on M (tokens in tiles of 16..256), 3 tokens on M with single CTAs only, 4 with CTA pairs only.
 // split_k > 1 (weights on M, residual, at most 256 tokens) divides K among CTAs and adds with
 // atomics.
-// residual == 2: the SwiGLU epilogue (no bias; out is bfloat16 [M, N/2]; N a multiple of 16).
+// residual == 2: the SwiGLU epilogue (no bias; out is bfloat16 [M, N/2]; N a multiple of 16); residual == 3: the same with
+// the tanh form of gelu on the gate.
 SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias, void* out, int out_dtype,
                                 int residual, int M, int N, int K, int lda, int ldo, int orientation,
                                 int split_k, int* status, cudaStream_t stream) {
-  const bool swiglu = residual == 2;
+  const bool swiglu = residual == 2 || residual == 3;
+  const int gate_gelu = residual == 3 ? 1 : 0;
   if (swiglu) {
     residual = 0;
     SPROUT_REQUIRE(N % 16 == 0 && !bias && out_dtype == SPROUT_BF16 && ldo >= N / 2 && ldo % 2 == 0,
@@ -572,6 +582,7 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
                  "(with tokens on M the kernel splits K by itself where that pays)");
 
   Params p;
+  p.gate_gelu = gate_gelu;
   p.bias = bias; p.out = out; p.out_is_f32 = out_dtype == SPROUT_F32;
   p.epilogue = swiglu ? EPI_SWIGLU : residual ? (split_k > 1 ? EPI_RESIDUAL_ATOMIC : EPI_RESIDUAL) : EPI_STORE;
   p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.status = status;
@@ -663,6 +674,7 @@ SPROUT_API int sprout_gemm_bf16_unscaled(const float* x, int ldx, const float* g
   SPROUT_REQUIRE(K % 8 == 0 && ldx % 4 == 0 && ldx >= K && ldo >= N, "gemm_bf16_unscaled: K (%d) must be a multiple of 8, the rows of x (%d) of 4", K, ldx);
   SPROUT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_bf16_unscaled: operands must be 16-byte aligned");
   Params p;
+  p.gate_gelu = 0;
   p.bias = nullptr; p.out = out; p.out_is_f32 = 1; p.epilogue = EPI_RESIDUAL_ATOMIC;
   p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.status = status;
   p.x32 = x; p.gain = gain; p.ldx = ldx;

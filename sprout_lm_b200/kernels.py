@@ -324,14 +324,17 @@ def attention_simple(q, k_cache, v_cache, block_table, seq_of_token, positions, 
          k_cache.shape[0], _ptr(status, "status", torch.int32), _stream())
 
 
-def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, split_k=1, swiglu=False):
+def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, split_k=1, swiglu=False, gate_activation="silu"):
     """out = a @ weight.T (+ bias) (+ residual) on the tcgen05 tensor cores; a and weight bfloat16.
 
     ``residual`` must be ``out`` itself (float32): the product is added in place.  orientation 0
     lets the kernel choose (weight rows on the MMA's M axis for up to 128 tokens), 1 forces
     tokens on M, 2 weights on M.  ``split_k`` > 1 divides K among CTAs (weights on M with a
     residual only; the partial sums are added with atomics).  ``swiglu``: weight rows interleave
-    gate and up in blocks of 8 and ``out`` is bfloat16 [M, N/2] = silu(gate) * up."""
+    gate and up in blocks of 8 and ``out`` is bfloat16 [M, N/2] = act(gate) * up, act = ``gate_activation``: "silu" or
+    "gelu_tanh" (the tanh form of gelu)."""
+    if gate_activation not in ("silu", "gelu_tanh"):
+        raise KernelError(f"gemm_bf16: the gated epilogue has silu and gelu_tanh, not {gate_activation!r}")
     _rows_contiguous(a, "a")
     _rows_contiguous(out, "out")
     if not weight.is_contiguous() or weight.dim() != 2:
@@ -347,7 +350,7 @@ def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, s
     if residual is not None and residual.data_ptr() != out.data_ptr():
         raise KernelError("gemm_bf16: the residual is added in place: pass out itself")
     _run("sprout_gemm_bf16", _ptr(a, "a"), _ptr(weight, "weight"), _ptr(bias, "bias", torch.float32, True),
-         _ptr(out, "out"), _dtype_code(out.dtype), 2 if swiglu else (1 if residual is not None else 0), M, N, K, a.stride(0),
+         _ptr(out, "out"), _dtype_code(out.dtype), (3 if gate_activation == "gelu_tanh" else 2) if swiglu else (1 if residual is not None else 0), M, N, K, a.stride(0),
          out.stride(0), orientation, split_k, _ptr(status, "status", torch.int32), _stream())
 
 
@@ -1475,10 +1478,9 @@ def gated_scan(q, k, v, z, bias, ctx, state, out, heads: int, groups: int, dim: 
     stride of one dtype.  Per key channel (default): z [tokens, heads * dim] (of that dtype or float32), a = sigmoid(z + bias)^(1 / tau), c = 1.
     ``per_head``: z [tokens, heads], dt = softplus(z + bias), a = exp(-exp(a_log) dt) for all of the head's channels, c = dt.
     ``given`` = (a, c), float32 [tokens, heads] each: the decay and the factor on k per head, ready-made (z and bias are None).
-    ``ones_col``: the state and the output have ``vdim`` columns of which the value rows fill all but the last block of up to
-    four: v is [tokens, heads * v_cols] with v_cols the largest multiple-of-4-aligned count below vdim that the caller
-    chose (``vdim - v.shape[1] // heads`` columns are extra), and column v_cols of the state is fed the constant 1, so that
-    column of the output is (sum of the decayed c k) . q.
+    ``ones_col``: the value rows are narrower than the state, v [tokens, heads * v_cols] with v_cols < vdim, and the state's
+    column v_cols is fed the constant 1 as a value (the columns after it 0): that column of the state is then the sum of the
+    decayed c k, and that column of the output its product with q_scale q, a normaliser.
     out float32 [tokens, heads * vdim].  A step whose longest portion has ``SCAN_CHUNKED_FROM`` tokens or more cuts the
     portions into chunks of ``SCAN_CHUNK`` tokens that are walked side by side (``SPROUT_GATED_SCAN=whole`` keeps one walk
     per request): scratch for every token's decay and every chunk's sums."""

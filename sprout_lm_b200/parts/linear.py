@@ -70,6 +70,13 @@ class Linear:
             kernels.swiglu(self.forward(a), out, block)
         return out
 
+    def forward_gated(self, a: torch.Tensor, activation: str) -> torch.Tensor:
+        """act(gate) * up of a fused gate/up matrix on the tensor-core path, in the product's epilogue (on the float32
+        accumulators): the rows interleave gate and up in blocks of 8; ``activation`` is "silu" or "gelu_tanh"."""
+        out = torch.empty((a.shape[0], self.out_features // 2), dtype=a.dtype, device=a.device)
+        kernels.gemm_bf16(a, self.weight, out, self.status, swiglu=True, gate_activation=activation)
+        return out
+
     def accumulate(self, a: torch.Tensor, acc: torch.Tensor) -> None:
         """acc (float32 [rows, out_features]) += a W^T, no bias: into a residual stream or a zeroed
         workspace.  bfloat16 weights only."""

@@ -182,8 +182,10 @@ class ClampedGLUMLP(Part):
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(Part):
     """x += W_down (act(W_gate h) * (W_up h)), no biases; ``activation`` is "silu", "gelu_tanh" (the tanh form of gelu) or
-    "gelu_erf" (the exact form).  Gate rows first, then up rows, in one fused product; the activation is a kernel of its
-    own (float32 arithmetic on the product's rounded results)."""
+    "gelu_erf" (the exact form).  One fused product for gate and up.  On the tensor-core path, for silu and the tanh form
+    of gelu and sizes in multiples of 8, the rows interleave gate and up in blocks of 8 and the activation runs in the
+    product's epilogue on the float32 accumulators; otherwise gate rows first, then up rows, and the activation is a
+    kernel of its own (float32 arithmetic on the product's results)."""
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh", names: dict | None = None):
         if hidden_size <= 0 or intermediate_size <= 0:
@@ -203,10 +205,18 @@ class GatedMLP(Part):
     def load(self, source: WeightSource):
         status = source.runtime.status
         gate, up = source.raw(self.names["gate"]), source.raw(self.names["up"])
-        self.gate_up = Linear(source.to_device_matrix(torch.cat([gate, up], dim=0)), None, status, any_inner_size=True)
+        self.in_epilogue = source.runtime.dtype == torch.bfloat16 and self.activation in ("silu", "gelu_tanh") \
+            and self.intermediate_size % INTERLEAVE == 0 and self.hidden_size % 8 == 0
+        fused = interleave_gate_up(gate, up, INTERLEAVE) if self.in_epilogue else torch.cat([gate, up], dim=0)
+        self.gate_up = Linear(source.to_device_matrix(fused), None, status, any_inner_size=True)
         self.down = Linear(source.matrix(self.names["down"]), None, status, any_inner_size=True)
 
     def forward(self, h, x, ctx=None):
+        if self.in_epilogue and h.stride(0) % 8 == 0:
+            self.down.forward(self.gate_up.forward_gated(h, self.activation), residual=x)
+            return
+        if self.in_epilogue:
+            raise RuntimeError("gated_mlp: the tensor-core path needs rows that start on 16-byte boundaries")
         gate_up = self.gate_up.forward(h)
         act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
         kernels.unit_act(gate_up, act, self.activation, gated=True)

@@ -62,7 +62,7 @@ def test_model_spec_follows_the_file():
     assert names["l1.mix.i"] == (3, 40) and names["l1.mix.f.b"] == (3,) and names["l1.mix.norm"] == (21,)
     assert names["l1.mlp.router"] == (6, 40) and names["l1.mlp.e5.up"] == (20, 40) and "l1.mlp.e0.gate" not in names
     assert names["l1.mlp.shared.sg"] == (1, 40) and names["l1.mlp.shared.down"] == (40, 12) and "l1.mlp.correction" not in names
-    assert "l2.mlp.gate" not in names and names["l3.mlp.gate"] == (24, 40)
+    assert "l2.mlp.gate" not in names and names["l3.mlp.gate"] == (27, 40)
 
 
 def test_a_model_without_loop_or_token_input():

@@ -113,6 +113,25 @@ def test_row_kernels(dtype):
         assert torch.equal(narrow.cpu(), torch.from_numpy(x).to(torch.bfloat16))
 
 
+def test_gated_gelu_in_the_products_epilogue():
+    """The dense feed-forward's first product with the tanh form of gelu on its accumulators (gate and up rows interleaved
+    in blocks of 8), for few tokens (weights on the MMA's rows) and many (tokens on them), beside silu."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.mlp import interleave_gate_up
+    rng = np.random.default_rng(6)
+    status = new_status()
+    for tokens, width, ff in ((5, 64, 48), (70, 128, 160), (300, 64, 256), (33, 40, 56)):
+        a = rounded(rng.normal(size=(tokens, width)), "bfloat16")
+        gate, up = rounded(rng.normal(0, 0.3, size=(ff, width)), "bfloat16"), rounded(rng.normal(0, 0.3, size=(ff, width)), "bfloat16")
+        fused = dev(interleave_gate_up(gate, up, 8), "bfloat16")
+        for name, fn in (("gelu_tanh", plain.gelu_tanh), ("silu", lambda z: z * plain.sigmoid(z))):
+            out = torch.empty(tokens, ff, dtype=torch.bfloat16, device=DEV)
+            kernels.gemm_bf16(dev(a, "bfloat16"), fused, out, status, swiglu=True, gate_activation=name)
+            want = fn(f64(a) @ f64(gate).T) * (f64(a) @ f64(up).T)
+            assert (np.abs(out.float().cpu().numpy() - want) <= 1e-2 * (1 + np.abs(want))).all(), (tokens, width, ff, name)
+    assert int(status.item()) == 0
+
+
 def _memory_inputs(rng, lengths, H, D, V, cap):
     """Projections and gate inputs per request; the forget gates run from fast to very slow, the input gates are wide, so
     the running maximum moves, and some steps push it far up."""

@@ -66,7 +66,7 @@ A = {"architecture": "Vuripel", "vocab": 203, "width": 40, "norm": {"eps": 1e-5}
          layer(attention_2(3, 3, 8, 12, 0.4, 2.0, (5, 2), (100.0, 4)), dense(56)),
          layer(mlstm(3, 12, 7, 3.0), moe(6, 2, 20, (3, 1), 12)),
          layer(attention(4, 2, 12, 6, 0.9, 1.2), None),
-         layer(mlstm(1, 20, 20), dense(24)),
+         layer(mlstm(1, 20, 20), dense(27)),
      ]}
 # no loop, no token input; a router without groups that takes one expert
 B = {"architecture": "Vuripel", "vocab": 190, "width": 64, "norm": {"eps": 1e-6},
