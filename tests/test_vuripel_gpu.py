@@ -297,7 +297,7 @@ ATTENTION_CASES = [
     (4, 2, 32, 64, 32, 16, 70, 3, 20.0, False, True),
     (8, 2, 64, 128, 0, 16, None, 0, 25.0, True, False),
     (4, 1, 64, 64, 48, 16, 100, 17, 40.0, False, True),
-    (8, 1, 64, 64, 16, 16, 130, 70, 50.0, True, True),
+    (8, 1, 64, 64, 32, 16, 130, 70, 45.0, True, True),
     (2, 2, 128, 128, 64, 32, 1, 1, 15.0, False, False),
 ]
 
