@@ -29,22 +29,21 @@ using namespace sprout_attn;
 
 namespace {
 
-// threads of a router block: 8 warps for 8 tokens; a block of one token (steps of few tokens, few blocks) takes 32 warps, so
-// that the router's rows are walked by as many warps as the SM holds
-__host__ __device__ constexpr int route_threads(int route_tokens) { return route_tokens == 1 ? 1024 : 256; }
+// threads of a router block: 32 warps, so that the router's rows are walked by as many warps as the SM holds (a block's time is
+// the latency of its rounds over the outputs: 33 outputs are 2 rounds of 32 warps, 5 of 8)
+constexpr int ROUTE_THREADS = 1024;
 
 // A block takes ROUTE_TOKENS tokens (8 in steps of many tokens, 1 in steps of few, where blocks are scarce; a token's
-// sums are the same in both): the warps share the router's outputs (warp w takes outputs w, w + 8, ...) and apply every
+// sums are the same in both): the 32 warps share the router's outputs (warp w takes outputs w, w + 32, ...) and apply every
 // weight they load to all 8 tokens; a lane sums every 32nd element, the lanes are added in a fixed order, so a token's
 // scores do not depend on the tokens beside it.  Warp t then takes token t's softmax and choices.
 template <typename T, int ROUTE_TOKENS>
-__global__ void __launch_bounds__(route_threads(ROUTE_TOKENS))
+__global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ router, const float* __restrict__ correction,
                  int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int tokens, int width,
                  int softmax_outputs, int experts, int top, float scale, int extra, float* __restrict__ extra_out,
                  int group_count, int group_keep, int renormalize) {
   extern __shared__ float smem[];
-  constexpr int ROUTE_THREADS = route_threads(ROUTE_TOKENS);
   int outputs = softmax_outputs + extra;              // rows of the router matrix
   float* zs = smem;                                   // ROUTE_TOKENS x outputs: scores
   float* choices = zs + ROUTE_TOKENS * outputs;       // ROUTE_TOKENS x outputs
@@ -590,7 +589,7 @@ SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const fl
   }
   dim3 grid((tokens + per_block - 1) / per_block);
 #define ROUTE(T, N)                                                                                                    \
-  sprout_launch(moe_route_kernel<T, N>, grid, dim3(route_threads(N)), smem, stream, (const T*)h, h_stride, router, correction, ids, \
+  sprout_launch(moe_route_kernel<T, N>, grid, dim3(ROUTE_THREADS), smem, stream, (const T*)h, h_stride, router, correction, ids, \
                 weights, counts, tokens, width, outputs, experts, top, scale, extra, extra_out, group_count, group_keep, renormalize)
   if (dtype == SPROUT_F32) {
     if (per_block == 1) ROUTE(float, 1); else ROUTE(float, 8);
