@@ -35,7 +35,8 @@ constexpr int ROUTE_THREADS = 1024;
 
 // A block takes ROUTE_TOKENS tokens (8 in steps of many tokens, 1 in steps of few, where blocks are scarce; a token's
 // sums are the same in both): the 32 warps share the router's outputs (warp w takes outputs w, w + 32, ...) and apply every
-// weight they load to all 8 tokens; a lane sums every 32nd element, the lanes are added in a fixed order, so a token's
+// weight they load to all 8 tokens; a lane sums its own elements in ascending order (four neighbours of every 128 where the rows
+// are multiples of four, else every 32nd), the lanes are added in a fixed order, so a token's
 // scores do not depend on the tokens beside it.  Warp t then takes token t's softmax and choices.
 template <typename T, int ROUTE_TOKENS>
 __global__ void __launch_bounds__(ROUTE_THREADS)
