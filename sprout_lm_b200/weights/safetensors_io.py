@@ -17,9 +17,9 @@ import numpy as np
 import torch
 
 MAX_HEADER_BYTES = 16 * 1024 * 1024
-_ITEM_BYTES = {"F32": 4, "BF16": 2, "F16": 2}
-_TORCH_DTYPE = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16}
-_NAME_OF = {torch.float32: "F32", torch.bfloat16: "BF16", torch.float16: "F16"}
+_ITEM_BYTES = {"F32": 4, "BF16": 2, "F16": 2, "I32": 4}
+_TORCH_DTYPE = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16, "I32": torch.int32}      # I32: integer tables
+_NAME_OF = {torch.float32: "F32", torch.bfloat16: "BF16", torch.float16: "F16", torch.int32: "I32"}
 
 
 class SafetensorsError(ValueError):
@@ -92,6 +92,8 @@ class SafetensorsFile:
             out = torch.from_numpy(raw.view("<f4").copy())
         elif kind == "F16":
             out = torch.from_numpy(raw.view("<f2").copy())
+        elif kind == "I32":
+            out = torch.from_numpy(raw.view("<i4").copy())
         else:
             out = torch.from_numpy(raw.view("<u2").copy().view(np.int16)).view(torch.bfloat16)
         return out.reshape(entry["shape"])
@@ -103,7 +105,7 @@ class SafetensorsFile:
 
 
 def write_safetensors(path, tensors: dict[str, torch.Tensor], metadata: dict | None = None) -> None:
-    """Write CPU tensors (float32, bfloat16 or float16) in the order given."""
+    """Write CPU tensors (float32, bfloat16, float16, or int32 for integer tables) in the order given."""
     header: dict = {}
     if metadata:
         header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}

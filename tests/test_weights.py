@@ -36,6 +36,13 @@ def test_round_trip_of_the_three_dtypes(tmp_path):
     np.testing.assert_array_equal(again["bf16"], tensors["bf16"].float().numpy())
 
 
+def test_integer_tables_round_trip(tmp_path):
+    table = torch.tensor([[0, -1, 2 ** 31 - 1], [7, -2 ** 31, 65536]], dtype=torch.int32)
+    write_safetensors(tmp_path / "t.safetensors", {"table": table, "w": torch.ones(2, dtype=torch.bfloat16)})
+    f = SafetensorsFile(tmp_path / "t.safetensors")
+    assert f.dtype("table") == torch.int32 and torch.equal(f.tensor("table"), table) and f.tensor("w").dtype == torch.bfloat16
+
+
 def test_malformed_files_are_refused(tmp_path):
     p = tmp_path / "m.safetensors"
     p.write_bytes(b"\x01\x00")
